@@ -1,0 +1,76 @@
+"""In-tree build of the CUDA library (sm_100a only).
+
+``build()`` compiles ``csrc/*.cu`` with nvcc into ``deepshift_b200/_lib/libdeepshift_b200.so``.
+The file is git-ignored but travels with the source tree, so a machine without nvcc can use
+a library built elsewhere from the same sources.
+"""
+import glob
+import hashlib
+import os
+import shutil
+import subprocess
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG, "csrc")
+LIB_DIR = os.path.join(PKG, "_lib")
+LIB_PATH = os.path.join(LIB_DIR, "libdeepshift_b200.so")
+STAMP = os.path.join(LIB_DIR, "sources.sha256")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]  # precise math throughout: never add --use_fast_math, the kernels rely on IEEE rounding
+
+
+def _sources():
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+
+
+def _digest():
+    h = hashlib.sha256()
+    files = _sources() + sorted(glob.glob(os.path.join(CSRC, "*.cuh")))
+    files.append(os.path.join(os.path.dirname(PKG), "include", "deepshift_b200.h"))
+    for f in files:
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_current():
+    try:
+        with open(STAMP) as fh:
+            return os.path.exists(LIB_PATH) and fh.read().strip() == _digest()
+    except OSError:
+        return False
+
+
+def nvcc_path():
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    return cand if os.path.exists(cand) else None
+
+
+def build(force=False, verbose=False, extra_flags=()):
+    """Compile the library if the sources changed.  Returns the library path."""
+    if not force and is_current():
+        return LIB_PATH
+    nvcc = nvcc_path()
+    if nvcc is None:
+        raise RuntimeError("nvcc not found and %s is missing or stale" % LIB_PATH)
+    os.makedirs(LIB_DIR, exist_ok=True)
+    env = dict(os.environ)
+    env.pop("CC", None)
+    env.pop("CXX", None)
+    cmd = [nvcc] + NVCC_FLAGS + list(extra_flags) + ["-ccbin", "g++", "-o", LIB_PATH] + _sources()
+    if verbose:
+        print(" ".join(cmd))
+    subprocess.run(cmd, check=True, env=env)
+    with open(STAMP, "w") as fh:
+        fh.write(_digest())
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    import sys
+    print(build(force=True, verbose=True, extra_flags=sys.argv[1:]))

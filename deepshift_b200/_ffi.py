@@ -1,0 +1,67 @@
+"""ctypes binding of the C ABI declared in include/deepshift_b200.h.
+
+There is no CPU fallback: if the CUDA library cannot be found or built, importing the
+symbols raises, and every wrapper raises ``RuntimeError`` on a non-zero status.
+"""
+import ctypes
+import os
+
+from . import _build
+
+_lib = None
+
+c_i32p = ctypes.POINTER(ctypes.c_int32)
+
+
+class Fuse(ctypes.Structure):
+    """Mirror of ``ds_fuse_t``."""
+    _fields_ = [
+        ("in_kind", ctypes.c_int), ("out_kind", ctypes.c_int),
+        ("act_integer_bits", ctypes.c_int), ("act_fraction_bits", ctypes.c_int),
+        ("relu", ctypes.c_int), ("requant", ctypes.c_int),
+        ("residual", ctypes.c_void_p), ("act_bits", ctypes.c_int),
+        ("reserved", ctypes.c_int * 4),
+    ]
+
+
+IN_I32, IN_F32_CONV, IN_F32_LINEAR = 0, 1, 2
+OUT_I32, OUT_F32 = 0, 1
+
+_VP, _I, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+_SIGNATURES = {
+    "ds_linear_i32": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP],
+    "ds_conv2d_i32": [_VP, _VP, _VP, _VP] + [_I] * 14 + [_VP],
+    "ds_linear_ex": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, ctypes.POINTER(Fuse), _VP],
+    "ds_conv2d_ex": [_VP, _VP, _VP, _VP] + [_I] * 13 + [ctypes.POINTER(Fuse), _VP],
+    "ds_compress": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
+    "ds_quantize_f32": [_VP, _VP, _LL, _I, _I, _I, _VP],
+    "ds_pipe_peak": [_I, _I, ctypes.POINTER(ctypes.c_double), _VP],
+}
+
+
+def lib():
+    """Loads (building first if the sources changed and nvcc is present) the CUDA library."""
+    global _lib
+    if _lib is None:
+        if not _build.is_current() and _build.nvcc_path() is not None:
+            _build.build()
+        if not os.path.exists(_build.LIB_PATH):
+            raise RuntimeError(
+                "deepshift_b200: CUDA library %s is missing and cannot be built (no nvcc); "
+                "there is no CPU fallback" % _build.LIB_PATH)
+        l = ctypes.CDLL(_build.LIB_PATH)
+        for name, args in _SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = ctypes.c_int
+        l.ds_strerror.argtypes = [ctypes.c_int]
+        l.ds_strerror.restype = ctypes.c_char_p
+        l.ds_version.restype = ctypes.c_int
+        _lib = l
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        raise RuntimeError("deepshift_b200.%s failed: %s (status %d)"
+                           % (what, lib().ds_strerror(status).decode(), status))

@@ -1,0 +1,174 @@
+// Weight packing, the standalone quantiser, the issue-rate probe and the status strings.
+#include "ds_common.cuh"
+
+namespace ds {
+namespace {
+
+// One thread per output word: OR together up to `num` (field, sign) pairs of one row.
+// Layout of the reference's COMPRESS helper (shift.cu:27-38): field in the low `bits`
+// bits of the slot, (sign > 0) in the bit above it.
+__global__ void compress_kernel(const int32_t* __restrict__ shiftp, const int32_t* __restrict__ sign,
+                                int32_t* __restrict__ packed, int OC, int K, int bits, int base, int num,
+                                int row_len)
+{
+    const long long total = (long long)OC * row_len;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int oc = int(i / row_len), w = int(i - (long long)oc * row_len);
+        const int k0 = w * num;
+        const int len = min(num, K - k0);
+        const int32_t* sp = shiftp + (long long)oc * K + k0;
+        const int32_t* gp = sign + (long long)oc * K + k0;
+        uint32_t value = 0;
+        int s = 0;
+        for (int j = 0; j < len; ++j) {
+            value |= uint32_t(__ldg(sp + j) - base) << s;
+            s += bits;
+            value |= uint32_t(__ldg(gp + j) > 0 ? 1 : 0) << s;
+            s += 1;
+        }
+        packed[i] = int32_t(value);
+    }
+}
+
+__global__ void quantize_kernel(const float* __restrict__ x, int32_t* __restrict__ out, long long n, int kind,
+                                Quant q)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float v = __ldg(x + i);
+        out[i] = (kind == DS_IN_F32_CONV) ? __float2int_rz(quant_conv_f(v, q)) : __float2int_rz(v * q.scale);
+    }
+}
+
+// ---- issue-rate probe: 16 independent chains per thread, register operands only ----------------
+constexpr int kChains = 16;
+
+template <int MODE>
+__global__ void __launch_bounds__(256) peak_kernel(int iters, int seed, int* sink)
+{
+    int s[4];
+    int mu[4];
+    float wf[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        s[j] = ((seed >> (3 * j)) & 7) + 1;  // shift amounts unknown to the compiler
+        mu[j] = ((seed >> j) & 1) ? 1 : -1;
+        wf[j] = __int_as_float(((127 - s[j]) << 23) | (((seed >> j) & 1) ? 0 : 0x80000000));
+    }
+    int a[kChains];
+    float f[kChains];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) {
+        a[c] = seed * (threadIdx.x + 1) + c * 977;
+        f[c] = kMagic + float(c);
+    }
+    const float xf = float(threadIdx.x) + 0.5f;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int c = 0; c < kChains; ++c) {
+                if (MODE == 0) a[c] = a[c] + (a[(c + 1) % kChains] >> s[r]);
+                else if (MODE == 1) a[c] = (a[(c + 1) % kChains] >> s[r]) * mu[r] + a[c];
+                else f[c] = __fmaf_rd(xf, wf[r], f[c]);
+            }
+    }
+    int r = 0;
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) r ^= (MODE == 2) ? __float_as_int(f[c]) : a[c];
+    if (r == 0x7fffffff) *sink = r;  // practically never; keeps the work alive
+}
+
+}  // namespace
+
+const char* status_string(int s)
+{
+    switch (s) {
+        case DS_OK: return "ok";
+        case DS_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or inconsistent shape)";
+        case DS_ERR_UNSUPPORTED: return "unsupported configuration (bits outside 1..7, base > 0, window > 31)";
+        case DS_ERR_CUDA: return "CUDA runtime error at launch";
+        case DS_ERR_RANGE: return "size exceeds 32-bit indexing limits of this build";
+        case DS_ERR_ALIGN: return "pointer not sufficiently aligned (outputs need 16 bytes)";
+        default: return "unknown status";
+    }
+}
+
+}  // namespace ds
+
+using namespace ds;
+
+extern "C" int ds_compress(const int32_t* shiftp, const int32_t* sign, int32_t* packed, int OC, int K,
+                           int bits, int base, void* stream)
+{
+    if (!shiftp || !sign || !packed || OC <= 0 || K <= 0) return DS_ERR_BAD_ARG;
+    if (bits < 1 || bits > 7) return DS_ERR_UNSUPPORTED;
+    const int num = 32 / (bits + 1);
+    const int row_len = (K + num - 1) / num;
+    const long long total = (long long)OC * row_len;
+    const int threads = 256;
+    const int blocks = int(total / threads + 1 > 148 * 16 ? 148 * 16 : total / threads + 1);
+    compress_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(shiftp, sign, packed, OC, K, bits,
+                                                                             base, num, row_len);
+    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
+extern "C" int ds_quantize_f32(const float* x, int32_t* out, long long n, int kind, int I, int F, void* stream)
+{
+    if (n < 0 || (n > 0 && (!x || !out))) return DS_ERR_BAD_ARG;
+    if (kind != DS_IN_F32_CONV && kind != DS_IN_F32_LINEAR) return DS_ERR_BAD_ARG;
+    if (F < 0 || F > 30 || (kind == DS_IN_F32_CONV && (I < 1 || I + F > 31))) return DS_ERR_BAD_ARG;
+    if (n == 0) return DS_OK;
+    Quant q;
+    q.scale = float(1ll << F);
+    q.sign_mode = (kind == DS_IN_F32_CONV && I == 1);
+    q.lo = q.hi = 0.f;
+    if (kind == DS_IN_F32_CONV) {
+        q.lo = -float(1ll << (I - 1 + F));
+        q.hi = float(((1ll << (I - 1)) - 1) * (1ll << F));
+    }
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
+    quantize_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, n, kind, q);
+    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
+extern "C" int ds_pipe_peak(int mode, int iters, double* ops_per_s, void* stream)
+{
+    if (!ops_per_s || iters <= 0 || mode < 0 || mode > 2) return DS_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return DS_ERR_CUDA;
+    int* sink = nullptr;
+    if (cudaMalloc(&sink, sizeof(int)) != cudaSuccess) return DS_ERR_CUDA;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    const int blocks = sms * 8, threads = 256;
+    auto run = [&](int n) {
+        if (mode == 0) peak_kernel<0><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
+        else if (mode == 1) peak_kernel<1><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
+        else peak_kernel<2><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
+    };
+    run(iters / 8 + 1);  // warm-up
+    cudaEventRecord(e0, st);
+    run(iters);
+    cudaEventRecord(e1, st);
+    int rc = DS_OK;
+    if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) rc = DS_ERR_CUDA;
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(sink);
+    if (rc == DS_OK && ms > 0.f)
+        *ops_per_s = double(blocks) * threads * double(iters) * 4.0 * kChains / (double(ms) * 1e-3);
+    return rc;
+}
+
+extern "C" const char* ds_strerror(int status) { return status_string(status); }
+extern "C" int ds_version(void) { return 100; }

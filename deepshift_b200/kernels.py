@@ -1,0 +1,194 @@
+"""Python operator layer: the reference's ``deepshift.kernels`` API on the B200 kernels.
+
+``linear``, ``conv2d`` and ``compress_sign_and_shift`` keep the names, argument order and
+return values of pytorch/deepshift/kernels/kernels.py:10,28,69.  They call the C ABI of
+include/deepshift_b200.h through ctypes on torch's current stream.  ``use_cuda=False`` raises:
+this package has no CPU path.
+
+Differences from the reference, all deliberate:
+  * the convolution reads the unpadded tensor (no ``F.pad`` copy, no im2col/col2im buffers);
+    ``padding=(ph, pw)`` pads H by ``ph`` and W by ``pw`` as ``torch.nn.functional.conv2d``
+    does (kernels.py:32-36 swaps the two for asymmetric padding);
+  * outputs are allocated with ``torch.empty`` (every element is written);
+  * kernels run on the current stream of the input's device, not the legacy default stream;
+  * a weight whose decoded right shift is >= 32 contributes exactly 0 (the zero-sign
+    encoding of utils.py:67-70; the reference CUDA kernel yields -1 for negative inputs);
+  * ``dilation != 1`` or ``groups != 1`` raises instead of being ignored (kernels.py:28).
+"""
+import torch
+
+from . import _ffi
+
+
+def _stream_ptr(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _check_tensor(t, name, dtype=None):
+    # The reference's CHECK_INPUT (shift_cuda.cpp:22-24) plus a dtype check it lacks.
+    if not t.is_cuda:
+        raise RuntimeError(name + " must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(name + " must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError("%s must be %s, got %s" % (name, dtype, t.dtype))
+
+
+def _pair(v):
+    if isinstance(v, int):
+        return (v, v)
+    v = tuple(int(e) for e in v)
+    return (v[0], v[0]) if len(v) == 1 else (v[0], v[1])
+
+
+def _no_cpu():
+    raise RuntimeError("deepshift_b200 has no CPU kernel path: use_cuda must be True")
+
+
+def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=False, requant=False,
+          residual=None, act_bits=0):
+    f = _ffi.Fuse()
+    f.in_kind, f.out_kind = in_kind, out_kind
+    f.act_integer_bits, f.act_fraction_bits = int(act_integer_bits), int(act_fraction_bits)
+    f.relu, f.requant = int(bool(relu)), int(bool(requant))
+    f.residual = residual.data_ptr() if residual is not None else None
+    f.act_bits = int(act_bits)
+    return f
+
+
+def linear(input, shift, sign, bias=None, conc_weight=None, use_cuda=True, act_bits=0):
+    """int32 [M,K] -> int32 [M,N].  ``shift``/``sign`` only give N (as in kernels.py:14)."""
+    if not use_cuda:
+        _no_cpu()
+    assert conc_weight is not None
+    _check_tensor(input, "input", torch.int32)
+    _check_tensor(conc_weight.data, "conc_weight.data", torch.int32)
+    if bias is not None:
+        _check_tensor(bias, "bias", torch.int32)
+    M, K = input.shape
+    N = shift.size(0)
+    out = torch.empty([M, N], dtype=torch.int32, device=input.device)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_linear_i32(input.data_ptr(), conc_weight.data.data_ptr(),
+                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                      M, K, N, conc_weight.bits, conc_weight.base, int(act_bits),
+                                      _stream_ptr(input.device))
+    _ffi.check(rc, "linear")
+    return out
+
+
+def _conv_geometry(input, shift, stride, padding, dilation, groups):
+    if _pair(dilation) != (1, 1) or groups != 1:
+        raise RuntimeError("the shift convolution kernel supports neither dilation nor groups")
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    B, C, H, W = input.shape
+    OC, KH, KW = shift.size(0), shift.size(2), shift.size(3)
+    OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
+    return B, C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW
+
+
+def conv2d(input, shift, sign, bias=None, conc_weight=None, stride=1, padding=0, dilation=1, groups=1,
+           use_cuda=True, act_bits=0):
+    """int32 NCHW (unpadded) -> int32 NCHW."""
+    if not use_cuda:
+        _no_cpu()
+    assert conc_weight is not None
+    _check_tensor(input, "input", torch.int32)
+    _check_tensor(conc_weight.data, "conc_weight.data", torch.int32)
+    if bias is not None:
+        _check_tensor(bias, "bias", torch.int32)
+    B, C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW = _conv_geometry(input, shift, stride, padding, dilation, groups)
+    out = torch.empty([B, OC, OH, OW], dtype=torch.int32, device=input.device)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_conv2d_i32(input.data_ptr(), conc_weight.data.data_ptr(),
+                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                      B, C, H, W, OC, KH, KW, sh, sw, ph, pw, conc_weight.bits,
+                                      conc_weight.base, int(act_bits), _stream_ptr(input.device))
+    _ffi.check(rc, "conv2d")
+    return out
+
+
+def compress_sign_and_shift(shift, sign, comp_size, base, bits, row_length, num):
+    """(shift', sign) int32 [OC,IC,KH,KW] -> packed int32 [comp_size] (kernels.py:69-74)."""
+    _check_tensor(shift, "shift", torch.int32)
+    _check_tensor(sign, "sign", torch.int32)
+    OC = shift.shape[0]
+    K = shift.numel() // OC
+    if num != 32 // (bits + 1) or row_length != (K + num - 1) // num or comp_size != row_length * OC:
+        raise RuntimeError("inconsistent packing geometry")
+    comp_weight = torch.empty([comp_size], dtype=torch.int32, device=shift.device)
+    with torch.cuda.device(shift.device):
+        rc = _ffi.lib().ds_compress(shift.data_ptr(), sign.data_ptr(), comp_weight.data_ptr(), OC, K,
+                                    bits, base, _stream_ptr(shift.device))
+    _ffi.check(rc, "compress_sign_and_shift")
+    return comp_weight
+
+
+# ------------------------------------------------------------------------------------------------
+# Fused forms used by the modules and the integer pipeline (no counterpart in the reference,
+# which runs the quantise / convert / ReLU steps as separate torch passes).
+
+def linear_fused(input, out_features, bias_i32, conc_weight, *, in_kind=_ffi.IN_I32, out_kind=_ffi.OUT_I32,
+                 act_integer_bits=16, act_fraction_bits=16, relu=False, requant=False, residual=None,
+                 act_bits=0):
+    _check_tensor(input, "input", torch.int32 if in_kind == _ffi.IN_I32 else torch.float32)
+    M, K = input.shape
+    out = torch.empty([M, out_features], device=input.device,
+                      dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
+    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_linear_ex(input.data_ptr(), conc_weight.data.data_ptr(),
+                                     bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),
+                                     M, K, out_features, conc_weight.bits, conc_weight.base, f,
+                                     _stream_ptr(input.device))
+    _ffi.check(rc, "linear_fused")
+    return out
+
+
+def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0, *, in_kind=_ffi.IN_I32,
+                 out_kind=_ffi.OUT_I32, act_integer_bits=16, act_fraction_bits=16, relu=False, requant=False,
+                 residual=None, act_bits=0):
+    _check_tensor(input, "input", torch.int32 if in_kind == _ffi.IN_I32 else torch.float32)
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    B, C, H, W = input.shape
+    OC, C2, KH, KW = weight_shape
+    if C2 != C:
+        raise RuntimeError("input has %d channels, weight expects %d" % (C, C2))
+    OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
+    out = torch.empty([B, OC, OH, OW], device=input.device,
+                      dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
+    if residual is not None:
+        _check_tensor(residual, "residual", torch.int32)
+        if residual.shape != out.shape:
+            raise RuntimeError("residual shape %s != output shape %s" % (tuple(residual.shape), tuple(out.shape)))
+    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_conv2d_ex(input.data_ptr(), conc_weight.data.data_ptr(),
+                                     bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),
+                                     B, C, H, W, OC, KH, KW, sh, sw, ph, pw, conc_weight.bits,
+                                     conc_weight.base, f, _stream_ptr(input.device))
+    _ffi.check(rc, "conv2d_fused")
+    return out
+
+
+def quantize(input, act_integer_bits, act_fraction_bits, like_conv=True):
+    """fp32 -> int32 fixed point in one pass (utils.py:7-21 + modules.py:153, or modules.py:25)."""
+    _check_tensor(input, "input", torch.float32)
+    out = torch.empty(input.shape, dtype=torch.int32, device=input.device)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_quantize_f32(input.data_ptr(), out.data_ptr(), input.numel(),
+                                        _ffi.IN_F32_CONV if like_conv else _ffi.IN_F32_LINEAR,
+                                        act_integer_bits, act_fraction_bits, _stream_ptr(input.device))
+    _ffi.check(rc, "quantize")
+    return out
+
+
+def pipe_peak(mode, iters=20000):
+    """Sustained shift-accumulate operations per second of one instruction mix (see the header)."""
+    import ctypes
+    v = ctypes.c_double(0.0)
+    rc = _ffi.lib().ds_pipe_peak(mode, iters, ctypes.byref(v), _stream_ptr(torch.cuda.current_device()))
+    _ffi.check(rc, "pipe_peak")
+    return v.value

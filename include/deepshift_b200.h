@@ -1,0 +1,139 @@
+/*
+ * deepshift_b200 -- C ABI of the B200 (sm_100a) shift-inference kernels.
+ *
+ * Drop-in boundary for DeepShift's `use_kernel=True` inference path.  Each entry point
+ * replaces one function of the reference's pybind module `deepshift_cuda`
+ * (pytorch/deepshift/kernels/cuda/shift_cuda.cpp:64-68) and is called by the Python shim
+ * deepshift_b200/kernels.py, which keeps the reference's `deepshift.kernels` signatures
+ * (pytorch/deepshift/kernels/kernels.py:10,28,69).
+ *
+ * Conventions
+ *   - Plain device pointers and sizes; the caller owns and allocates every buffer.  The
+ *     library allocates nothing on these paths and keeps no state between calls.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  Work is
+ *     enqueued on it and the call returns without synchronising.  The current CUDA device
+ *     must be the one that owns the pointers.
+ *   - Every function returns a ds_status (0 = success).  No device-side assert or trap.
+ *   - int32 tensors are two's-complement; sums wrap modulo 2^32 exactly as the reference.
+ *
+ * Packed weights ("ConcWeight", pytorch/deepshift/utils.py:54-88, shift.cu:27-55)
+ *   num = 32 / (bits + 1) weights per int32 word, row_len = ceil(K / num) words per output
+ *   row; weight i of a word sits in bits [i*(bits+1), i*(bits+1)+bits) as `field` and bit
+ *   i*(bits+1)+bits as `positive`.  Decoded right shift r = field + base, sign = positive ?
+ *   +1 : -1.  r in [0,31]: term = sign*(x >> r) (arithmetic shift, negate AFTER the shift);
+ *   r < 0: term = sign*(x << -r); r >= 32: term = 0 (the zero-weight encoding).
+ */
+#ifndef DEEPSHIFT_B200_H
+#define DEEPSHIFT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    DS_OK = 0,
+    DS_ERR_BAD_ARG = 1,      /* null pointer, non-positive size, inconsistent shape      */
+    DS_ERR_UNSUPPORTED = 2,  /* bits outside 1..7, base > 0, kernel window > 31, ...     */
+    DS_ERR_CUDA = 3,         /* the CUDA runtime reported an error at launch              */
+    DS_ERR_RANGE = 4,        /* a size exceeds what 32-bit indexing of this build allows  */
+    DS_ERR_ALIGN = 5         /* a pointer is not 16-byte aligned                          */
+} ds_status;
+
+/* Input element kinds of the *_ex entry points. */
+enum {
+    DS_IN_I32 = 0,       /* int32 fixed point (what the reference kernels receive)                         */
+    DS_IN_F32_CONV = 1,  /* fp32, quantised in the kernel as Conv2dShift does: clamp(floor(x*2^F)) -- utils.py:7-21, modules.py:153,317 */
+    DS_IN_F32_LINEAR = 2 /* fp32, quantised as LinearShift does: trunc(x*2^F), no clamp -- modules.py:25 */
+};
+
+/* Output element kinds of the *_ex entry points. */
+enum {
+    DS_OUT_I32 = 0, /* int32 accumulator + bias (what the reference kernels write)     */
+    DS_OUT_F32 = 1  /* float(acc) / 2^F, the conversion of modules.py:30-31,161-162      */
+};
+
+/*
+ * Optional fused prologue/epilogue of ds_linear_ex / ds_conv2d_ex.  Zero-initialise for the
+ * plain int32-in / int32-out behaviour.  Order of the epilogue on v = acc + bias:
+ *   residual add -> ReLU -> requantise clamp -> store.
+ */
+typedef struct {
+    int in_kind;            /* DS_IN_*                                                     */
+    int out_kind;           /* DS_OUT_*                                                    */
+    int act_integer_bits;   /* I of round_to_fixed; used by DS_IN_F32_CONV and `requant`   */
+    int act_fraction_bits;  /* F; used by every fp32 conversion                            */
+    int relu;               /* v = max(v, 0)                                               */
+    int requant;            /* v = clamp(v, -2^(I-1+F), (2^(I-1)-1)*2^F): what the next
+                               Conv2dShift's round_to_fixed would do to v/2^F              */
+    const int32_t *residual;/* same shape/layout as the output, added before ReLU; may be NULL */
+    int act_bits;           /* caller's guarantee on int32 inputs: every x satisfies
+                               -2^(act_bits-1) <= x <= 2^(act_bits-1).  0 = no guarantee
+                               (exact integer path).  1..20 enables the FP32-pipe path.
+                               Implied by DS_IN_F32_CONV (I+F).                            */
+    int reserved[4];
+} ds_fuse_t;
+
+/*
+ * Shift "GEMM": out[m,n] = bias[n] + sum_k term(x[m,k], weight[n,k]).
+ * Replaces DEEP_SHIFT_LINEAR (shift_cuda.cpp:26-39 -> shift.cu:174-387, kernel :57-120).
+ *   x [M,K] int32 row-major, packed [N, ceil(K/num)] int32, bias [N] int32 or NULL,
+ *   out [M,N] int32 row-major (need not be zero-initialised).
+ * act_bits: see ds_fuse_t.act_bits.
+ */
+int ds_linear_i32(const int32_t *x, const int32_t *packed, const int32_t *bias, int32_t *out,
+                  int M, int K, int N, int bits, int base, int act_bits, void *stream);
+
+/*
+ * Shift convolution on the UNPADDED NCHW input (zero padding is implicit).
+ * Replaces F.pad + DEEP_SHIFT_CONV (kernels.py:32-53, shift_cuda.cpp:41-53 ->
+ * shift.cu:399-669: IM2COL :122-153, GEMM :57-120, COL2IM :155-172) without the im2col and
+ * col2im buffers.  K = C*KH*KW flattened in (ic,kh,kw) order; OH = (H+2ph-KH)/sh+1.
+ *   x [B,C,H,W] int32, packed [OC, ceil(K/num)], bias [OC] or NULL, out [B,OC,OH,OW] int32.
+ * No dilation, no groups (the reference ignores both, kernels.py:28).
+ */
+int ds_conv2d_i32(const int32_t *x, const int32_t *packed, const int32_t *bias, int32_t *out,
+                  int B, int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph,
+                  int pw, int bits, int base, int act_bits, void *stream);
+
+/* As above with a fused prologue/epilogue.  x is int32 or fp32 per fuse->in_kind, out is
+ * int32 or fp32 per fuse->out_kind. */
+int ds_linear_ex(const void *x, const int32_t *packed, const int32_t *bias, void *out, int M,
+                 int K, int N, int bits, int base, const ds_fuse_t *fuse, void *stream);
+int ds_conv2d_ex(const void *x, const int32_t *packed, const int32_t *bias, void *out, int B,
+                 int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
+                 int bits, int base, const ds_fuse_t *fuse, void *stream);
+
+/*
+ * Packs (shift', sign) into words.  Replaces COMPRESS_SIGN_SHIFT (shift_cuda.cpp:55-61 ->
+ * shift.cu:388-397, one launch per output channel there; one launch in total here).
+ *   shiftp, sign [OC,K] int32; packed [OC, ceil(K/num)] int32; field = shiftp - base.
+ */
+int ds_compress(const int32_t *shiftp, const int32_t *sign, int32_t *packed, int OC, int K,
+                int bits, int base, void *stream);
+
+/*
+ * round_to_fixed(x, I, F) * 2^F as int32 (utils.py:7-21 + modules.py:153), one pass.
+ * kind = DS_IN_F32_CONV (floor + clamp) or DS_IN_F32_LINEAR (trunc, no clamp, modules.py:25).
+ */
+int ds_quantize_f32(const float *x, int32_t *out, long long n, int kind, int act_integer_bits,
+                    int act_fraction_bits, void *stream);
+
+/*
+ * Register-only issue-rate probe used for the roofline denominator.
+ *   mode 0: shift + add (both on the integer ALU pipe)
+ *   mode 1: shift + integer multiply-add (ALU pipe + FMA pipe)
+ *   mode 2: FP32 fused multiply-add with round-down (FMA pipe)
+ * Runs on `stream`, synchronises, and writes the sustained rate in shift-accumulate
+ * operations per second (one op = one shift plus one signed accumulate) to *ops_per_s.
+ */
+int ds_pipe_peak(int mode, int iters, double *ops_per_s, void *stream);
+
+const char *ds_strerror(int status);
+int ds_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPSHIFT_B200_H */
