@@ -19,6 +19,8 @@
 //     rounding that floor.  The "-1" of every negative weight is a per-output constant that
 //     the epilogue adds back, and the accumulator is drained into an int32 register often
 //     enough that |A| stays below 2^22.  Needs base == 0 and a bound on |x| (act_bits).
+#include <type_traits>
+
 #include "ds_common.cuh"
 
 namespace ds {
@@ -50,8 +52,10 @@ struct GemmParams {
 };
 
 struct KEntry {
-    int off;   // ic*H*W + kh*W + kw
-    int khkw;  // kh | kw << 8; kh = 31 marks k >= K
+    int off;  // ic*H*W + kh*W + kw
+    int kh;   // 31 marks k >= K (bit 31 of a row mask is never set)
+    int kw;
+    int pad;
 };
 
 template <int TMG, int TNG, int TN, int BKT, bool FP>
@@ -59,29 +63,31 @@ struct Smem {
     static constexpr int BM = TMG * kTM;
     static constexpr int BN = TNG * TN;
     static constexpr int AP = BM + 4;
-    float a[2][BKT][AP];                 // FP: x + 0.5 as float; integer path: x as int bits
-    float b[2][BKT][BN];                 // FP: +-2^-r; integer path: shift amounts (int bits)
+    float a[2][BKT][AP];  // FP: x + 0.5 as float; integer path: x (int bits)
+    float b[2][BKT][BN];  // FP: +-2^-r; integer path: shift amounts (int bits)
     int bm[FP ? 1 : 2][FP ? 1 : BKT][FP ? 1 : BN];  // integer path: multipliers
     KEntry ktab[2][BKT];
-    int negc[BN];                        // FP: number of negative weights per output column
+    int lut0[256];             // decoded weight per field value: FP float bits / integer shift
+    int lut1[FP ? 1 : 256];    // integer path: multiplier
+    int negc[BN];              // FP: negative weights per output column
+    int accs[FP ? kTM * TN * kThreads : 1];  // FP: drained accumulators, [slot][thread]
 };
 
-template <int TN>
-struct Frag {
-    float v[TN];
-};
+__device__ __forceinline__ void red_shared_add(int* addr, int v)
+{
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(addr)), "r"(v) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------
 template <int TMG, int TNG, int TN, int BKT, bool FP, bool CONV>
-__global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmParams p)
+__global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
 {
     using S = Smem<TMG, TNG, TN, BKT, FP>;
     constexpr int BM = S::BM, BN = S::BN;
-    constexpr int EA = BM * BKT / kThreads;  // x elements staged per thread per tile
-    constexpr int EW = (BN * BKT / 4 + kThreads - 1) / kThreads;  // words per thread (num >= 4)
+    constexpr int EW = (BN * (BKT / 4) + kThreads - 1) / kThreads;  // words per thread (num >= 4)
     static_assert(TMG * TNG == kThreads, "256 threads");
     static_assert(TN == 4 || TN == 8, "TN");
-    static_assert(EA >= 1 && EA <= 16, "staging registers");
+    static_assert((BN & (BN - 1)) == 0, "BN power of two");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     S& s = *reinterpret_cast<S*>(smem_raw);
@@ -95,22 +101,21 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
     const int tn = CONV ? (t / TMG) : (t % TNG);
 
     // ---- per-thread staging geometry -------------------------------------------------------
-    // CONV: thread stages column k_local = t / BM + (256 / BM) * e of row m_local = t % BM.
-    // LINEAR: k_local = t % BKT, m_local = t / BKT + (256 / BKT) * e  (k is contiguous in x).
-    const int a_m = CONV ? (t % BM) : (t / BKT);
-    const int a_k = CONV ? (t / BM) : (t % BKT);
-    constexpr int A_MSTEP = CONV ? 0 : (kThreads / BKT);
-    constexpr int A_KSTEP = CONV ? ((kThreads >= BM) ? kThreads / BM : 1) : 0;
-    constexpr int A_ELEMS = CONV ? (BKT / A_KSTEP) : EA;
+    // CONV: one row m_local = t % BM, columns k_local = t / BM + (256 / BM) * e.
+    // LINEAR: one column k_local = t % KL, rows m_local = t / KL + (256 / KL) * e, KL = 32 or 16
+    //         (k is contiguous in x, so a warp reads whole sectors).
+    constexpr int KL = (BKT > 16) ? 32 : 16;
+    constexpr int A_MSTEP = kThreads / KL;
+    constexpr int A_KSTEP = (kThreads >= BM) ? kThreads / BM : 1;
+    constexpr int A_ELEMS = CONV ? (BKT + A_KSTEP - 1) / A_KSTEP : BM / A_MSTEP;
     static_assert(A_ELEMS <= 16, "staging registers");
-    static_assert(!CONV || kThreads >= BM || true, "");
+    const int a_m = CONV ? (t % BM) : (t / KL);
+    const int a_k = CONV ? (t / BM) : (t % KL);
 
     const int32_t* xi = static_cast<const int32_t*>(p.x);
-    const float* xf = static_cast<const float*>(p.x);
-    long long x_base = 0;       // CONV: element offset of (b, 0, ih0, iw0)
-    uint32_t rowmask = 0, colmask = 0;
+    long long x_base = 0;  // CONV: element offset of (b, 0, ih0, iw0); LINEAR: of (m0 + a_m, a_k)
+    uint32_t rowmask = 0, colmask = 0;  // CONV: valid kh / kw; LINEAR: rowmask bit e = row valid
     if (CONV) {
-        // BM can exceed 256 only if a thread owned several rows; not instantiated.
         const int m = m0 + a_m;
         if (m < p.M) {
             const int b = m / p.P, pp = m - b * p.P;
@@ -122,81 +127,102 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
                 if (unsigned(iw0 + kw) < unsigned(p.W)) colmask |= 1u << kw;
             x_base = (long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0;
         }
+    } else {
+        x_base = (long long)(m0 + a_m) * p.K + a_k;
+#pragma unroll
+        for (int e = 0; e < A_ELEMS; ++e)
+            if (m0 + a_m + e * A_MSTEP < p.M) rowmask |= 1u << e;
+        if (a_k >= p.bk) rowmask = 0;
     }
 
-    // ---- accumulators ----------------------------------------------------------------------
-    int acc[kTM][TN];
-    float accf[FP ? kTM : 1][FP ? TN : 1];
-#pragma unroll
-    for (int i = 0; i < kTM; ++i)
-#pragma unroll
-        for (int j = 0; j < TN; ++j) {
-            acc[i][j] = 0;
-            if (FP) accf[i][j] = kMagic;
+    // ---- decode table, accumulators ------------------------------------------------------------
+    for (int f = t; f < (1 << p.dec.fw); f += kThreads) {
+        if (FP) {
+            int neg;
+            s.lut0[f] = __float_as_int(decode_f32(uint32_t(f), p.dec, true, neg));
+        } else {
+            int shv, mul;
+            decode_int(uint32_t(f), p.dec, true, shv, mul);
+            s.lut0[f] = shv;
+            s.lut1[f] = mul;
         }
-    if (FP)
+    }
+    int acc[FP ? 1 : kTM][FP ? 1 : TN];
+    float accf[FP ? kTM : 1][FP ? TN : 1];
+    if (FP) {
+#pragma unroll
+        for (int i = 0; i < kTM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                accf[i][j] = kMagic;
+                s.accs[(i * TN + j) * kThreads + t] = 0;
+            }
         for (int i = t; i < BN; i += kThreads) s.negc[i] = 0;
+    } else {
+#pragma unroll
+        for (int i = 0; i < kTM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) acc[i][j] = 0;
+    }
 
     // ---- staging helpers -------------------------------------------------------------------
     int a_reg[A_ELEMS];
     uint32_t w_reg[EW];
+    const int nwords = BN * p.kt_words;
 
     auto fill_ktab = [&](int tile, int buf) {
-        if (CONV && t < p.bk) {
+        if (CONV && t < BKT) {
             const int k = tile * p.bk + t;
             KEntry e;
-            if (k < p.K) {
+            e.pad = 0;
+            if (t < p.bk && k < p.K) {
                 const int khw = p.KH * p.KW;
                 const int ic = k / khw, tap = k - ic * khw;
-                const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                e.off = ic * p.H * p.W + kh * p.W + kw;
-                e.khkw = kh | (kw << 8);
+                e.kh = tap / p.KW;
+                e.kw = tap - e.kh * p.KW;
+                e.off = ic * p.H * p.W + e.kh * p.W + e.kw;
             } else {
                 e.off = 0;
-                e.khkw = 31;
+                e.kh = 31;
+                e.kw = 0;
             }
             s.ktab[buf][t] = e;
         }
     };
 
-    // Raw fetch of tile `tile` into registers (x as int bits of the quantised value).
+    // Raw fetch of tile `tile` into registers.  fp32 inputs keep their bits; positions outside
+    // the image or the matrix carry a marker so that stash() stores the integer 0 there
+    // without quantising it.
     auto fetch = [&](int tile, int buf) {
-        const int k0 = tile * p.bk;
+        const int padv = (p.in_kind == DS_IN_I32) ? 0 : kPadMarker;
+        if (CONV) {
 #pragma unroll
-        for (int e = 0; e < A_ELEMS; ++e) {
-            // fp32 inputs: positions outside the image or the matrix carry a marker (a NaN
-            // pattern) so that stash() stores the integer 0 there without quantising it.
-            int v = (p.in_kind == DS_IN_I32) ? 0 : kPadMarker;
-            if (CONV) {
+            for (int e = 0; e < A_ELEMS; ++e) {
                 const int kl = a_k + e * A_KSTEP;
-                if (kl < p.bk) {
-                    const KEntry ke = s.ktab[buf][kl];
-                    const int kh = ke.khkw & 0xff, kw = ke.khkw >> 8;
-                    if (((rowmask >> kh) & (colmask >> kw) & 1u) != 0u) {
-                        const long long idx = x_base + ke.off;
-                        if (p.in_kind == DS_IN_I32) v = __ldg(xi + idx);
-                        else v = __float_as_int(__ldg(xf + idx));
-                    }
+                int v = padv;
+                if (kl < BKT) {
+                    const int4 ke = *reinterpret_cast<const int4*>(&s.ktab[buf][kl]);
+                    if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u) v = __ldg(xi + (x_base + ke.x));
                 }
-            } else {
-                const int ml = a_m + e * A_MSTEP;
-                const int m = m0 + ml, k = k0 + a_k;
-                if (a_k < p.bk && m < p.M && k < p.K) {
-                    const long long idx = (long long)m * p.K + k;
-                    if (p.in_kind == DS_IN_I32) v = __ldg(xi + idx);
-                    else v = __float_as_int(__ldg(xf + idx));
-                }
+                a_reg[e] = v;
             }
-            a_reg[e] = v;
+        } else {
+            const int32_t* src = xi + (x_base + (long long)tile * p.bk);
+            const bool ktail = (tile * p.bk + a_k) >= p.K;
+#pragma unroll
+            for (int e = 0; e < A_ELEMS; ++e) {
+                int v = padv;
+                if (((rowmask >> e) & 1u) && !ktail) v = __ldg(src + (long long)e * A_MSTEP * p.K);
+                a_reg[e] = v;
+            }
         }
         const int w0 = tile * p.kt_words;
-        const int nwords = BN * p.kt_words;
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
             const int wi = t + e * kThreads;
             uint32_t w = 0;
             if (wi < nwords) {
-                const int n = wi % BN, jw = wi / BN;
+                const int n = wi & (BN - 1), jw = wi / BN;
                 if (n0 + n < p.N && w0 + jw < p.dec.row_len)
                     w = uint32_t(__ldg(p.packed + (long long)(n0 + n) * p.dec.row_len + w0 + jw));
             }
@@ -204,61 +230,75 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
         }
     };
 
+    auto to_smem_value = [&](int v) -> float {
+        if (p.in_kind == DS_IN_I32) {
+            // x + 0.5 without an int->float conversion: adding 2x+1 to the bits of
+            // 1.5*2^22 (ulp 0.5) gives 1.5*2^22 + x + 0.5 exactly for |x| < 2^20.
+            return FP ? (__int_as_float(2 * v + (kHalfMagicBits + 1)) - kHalfMagic) : __int_as_float(v);
+        }
+        float f;  // the quantised value, an integer held in a float
+        if (v == kPadMarker) f = 0.f;
+        else if (p.in_kind == DS_IN_F32_CONV) f = quant_conv_f(__int_as_float(v), p.q);
+        else f = truncf(__int_as_float(v) * p.q.scale);
+        return FP ? (f + 0.5f) : __int_as_float(__float2int_rz(f));
+    };
+
+    // Decode `NUM` fields of one word into column n of the weight tile.
+    auto decode_word = [&](auto num_tag, uint32_t w, int buf, int krow, int n, int klive) {
+        constexpr int NUM = decltype(num_tag)::value;
+        const uint32_t fmask = (1u << p.dec.fw) - 1u;
+        int negs = 0;
+#pragma unroll
+        for (int i = 0; i < NUM; ++i) {
+            const uint32_t f = w & fmask;
+            w >>= p.dec.fw;
+            int v0 = s.lut0[f];
+            if (i >= klive) v0 = 0;  // k >= K: the tail slots of the last word
+            s.b[buf][krow + i][n] = __int_as_float(v0);
+            if (FP) {
+                negs += int(uint32_t(v0) >> 31);
+            } else {
+                int v1 = s.lut1[f];
+                if (i >= klive) v1 = 0;
+                s.bm[buf][krow + i][n] = v1;
+            }
+        }
+        if (FP && negs) atomicAdd(&s.negc[n], negs);
+    };
+
     // Convert and store the registers of tile `tile` into shared buffer `buf`.
     auto stash = [&](int tile, int buf) {
-        const int k0 = tile * p.bk;
 #pragma unroll
         for (int e = 0; e < A_ELEMS; ++e) {
             const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
             const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
-            if (kl < p.bk) {
-                const int v = a_reg[e];
-                float o;
-                if (p.in_kind == DS_IN_I32) {
-                    // x + 0.5 without an int->float conversion: adding 2x+1 to the bits of
-                    // 1.5*2^22 (ulp 0.5) gives 1.5*2^22 + x + 0.5 exactly for |x| < 2^20.
-                    o = FP ? (__int_as_float(2 * v + (kHalfMagicBits + 1)) - kHalfMagic) : __int_as_float(v);
-                } else {
-                    float f;  // the quantised value, an integer held in a float
-                    if (v == kPadMarker) f = 0.f;
-                    else if (p.in_kind == DS_IN_F32_CONV) f = quant_conv_f(__int_as_float(v), p.q);
-                    else f = truncf(__int_as_float(v) * p.q.scale);
-                    o = FP ? (f + 0.5f) : __int_as_float(__float2int_rz(f));
-                }
-                s.a[buf][kl][ml] = o;
-            }
+            if (kl < BKT) s.a[buf][kl][ml] = to_smem_value(a_reg[e]);
         }
-        const int nwords = BN * p.kt_words;
+        const int k0 = tile * p.bk;
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
             const int wi = t + e * kThreads;
             if (wi < nwords) {
-                const int n = wi % BN, jw = wi / BN;
-                uint32_t w = w_reg[e];
-                const int kbase = jw * p.dec.num;
-                int negs = 0;
-                for (int i = 0; i < p.dec.num; ++i) {
-                    const bool live = (k0 + kbase + i) < p.K;
-                    if (FP) {
-                        int neg;
-                        s.b[buf][kbase + i][n] = decode_f32(w, p.dec, live, neg);
-                        negs += neg;
-                    } else {
-                        int shv, mul;
-                        decode_int(w, p.dec, live, shv, mul);
-                        s.b[buf][kbase + i][n] = __int_as_float(shv);
-                        s.bm[buf][kbase + i][n] = mul;
-                    }
-                    w >>= p.dec.fw;
+                const int n = wi & (BN - 1), jw = wi / BN;
+                const int krow = jw * p.dec.num;
+                const int klive = p.K - (k0 + krow);  // fields below this index are real weights
+                const uint32_t w = w_reg[e];
+                switch (p.dec.num) {
+                    case 4: decode_word(std::integral_constant<int, 4>(), w, buf, krow, n, klive); break;
+                    case 5: decode_word(std::integral_constant<int, 5>(), w, buf, krow, n, klive); break;
+                    case 6: decode_word(std::integral_constant<int, 6>(), w, buf, krow, n, klive); break;
+                    case 8: decode_word(std::integral_constant<int, 8>(), w, buf, krow, n, klive); break;
+                    case 10: decode_word(std::integral_constant<int, 10>(), w, buf, krow, n, klive); break;
+                    default: decode_word(std::integral_constant<int, 16>(), w, buf, krow, n, klive); break;
                 }
-                if (FP && negs) atomicAdd(&s.negc[n], negs);
             }
         }
     };
 
     auto compute = [&](int buf) {
-#pragma unroll 4
-        for (int k = 0; k < p.bk; ++k) {
+#pragma unroll
+        for (int k = 0; k < BKT; ++k) {
+            if (k >= p.bk) break;
             float a[kTM];
             *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[buf][k][4 * tm]);
             *reinterpret_cast<float4*>(&a[4]) =
@@ -288,14 +328,18 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
         }
     };
 
+    // FP path: move the float accumulators (raw bits, kMagicBits + A) into this thread's
+    // shared int32 slots and restart them; the epilogue removes ndrains * kMagicBits.
+    int ndrains = 0;
     auto drain = [&]() {
 #pragma unroll
         for (int i = 0; i < kTM; ++i)
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
-                acc[i][j] += __float_as_int(accf[i][j]) - kMagicBits;
+                red_shared_add(&s.accs[(i * TN + j) * kThreads + t], __float_as_int(accf[i][j]));
                 accf[i][j] = kMagic;
             }
+        ++ndrains;
     };
 
     // ---- main loop: two shared buffers, register prefetch, one barrier per tile --------------
@@ -321,12 +365,16 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
         }
         __syncthreads();
     }
-    if (FP) drain();
+    if (FP) drain();  // each thread reads back only its own slots below
 
     // ---- epilogue -----------------------------------------------------------------------------
     // Column index of accumulator j and row index of accumulator i inside the CTA tile.
     auto ncol = [&](int j) { return (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j); };
     auto mrow = [&](int i) { return (i >= 4) ? (BM / 2 + 4 * tm + i - 4) : (4 * tm + i); };
+    auto accv = [&](int i, int j) -> int {
+        if (FP) return s.accs[(i * TN + j) * kThreads + t] - ndrains * kMagicBits;
+        return acc[FP ? 0 : i][FP ? 0 : j];
+    };
 
     int addc[TN];
 #pragma unroll
@@ -368,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
                     const long long o = ((long long)b * p.OC + n) * p.P + pp;
                     int v[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = finish(acc[4 * h + i][j] + addc[j], o + i);
+                    for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j) + addc[j], o + i);
                     if (p.out_kind == DS_OUT_I32) {
                         *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
                     } else {
@@ -388,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
                         const int n = n0 + ncol(j);
                         if (n >= p.N) continue;
                         const long long o = ((long long)b * p.OC + n) * p.P + pp;
-                        const int v = finish(acc[4 * h + i][j] + addc[j], o);
+                        const int v = finish(accv(4 * h + i, j) + addc[j], o);
                         if (p.out_kind == DS_OUT_I32) oi[o] = v;
                         else of[o] = __int2float_rn(v) * p.inv_scale;
                     }
@@ -408,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
                 if (vec && n + 3 < p.N) {
                     int v[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = finish(acc[i][4 * h + j] + addc[4 * h + j], o + j);
+                    for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
                     if (p.out_kind == DS_OUT_I32) {
                         *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
                     } else {
@@ -420,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, FP ? 1 : 2) gemm_kernel(const GemmPa
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (n + j >= p.N) continue;
-                        const int v = finish(acc[i][4 * h + j] + addc[4 * h + j], o + j);
+                        const int v = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
                         if (p.out_kind == DS_OUT_I32) oi[o + j] = v;
                         else of[o + j] = __int2float_rn(v) * p.inv_scale;
                     }
@@ -461,8 +509,8 @@ int launch_path(GemmParams& p, cudaStream_t st)
 {
     // Tile shape by output width: 128x128 for wide layers, 256x64 for 64-channel layers,
     // 256x32 below that; 64x128 when there are few rows (small-batch linear layers).
-    if (!CONV && p.M <= 64) return launch_cfg<8, 32, 4, 32, FP, CONV>(p, st);
-    if (p.N > 64) return launch_cfg<16, 16, 8, 32, FP, CONV>(p, st);
+    if (!CONV && p.M <= 64) return launch_cfg<8, 32, 4, 20, FP, CONV>(p, st);
+    if (p.N > 64) return launch_cfg<16, 16, 8, 20, FP, CONV>(p, st);
     if (p.N > 32) return launch_cfg<32, 8, 8, 16, FP, CONV>(p, st);
     return launch_cfg<32, 8, 4, 16, FP, CONV>(p, st);
 }
@@ -501,7 +549,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.rq_hi = int(hi);
     }
     // FP32-pipe path: needs base == 0 and every |x| <= 2^(act_bits-1) <= 2^19, and at least
-    // one k-tile (<= 32 terms of magnitude <= 2^(act_bits-1) + 1) between drains.
+    // one k-tile (<= 20 terms of magnitude <= 2^(act_bits-1) + 1) between drains.
     int ab = f.act_bits;
     if (f.in_kind == DS_IN_F32_CONV) ab = p.q.sign_mode ? F + 2 : I + F;
     if (f.in_kind == DS_IN_F32_LINEAR) ab = 0;
@@ -509,7 +557,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     if (use_fp) {
         const long long per_term = (1ll << (ab - 1)) + 1;
         const long long terms = ((1ll << 22) - 1) / per_term;  // terms that cannot overflow
-        p.flush_tiles = int(terms / 32 > 1024 ? 1024 : terms / 32);  // tiles of <= 32 terms
+        p.flush_tiles = int(terms / 20 > 1024 ? 1024 : terms / 20);  // tiles of <= 20 terms
         if (p.flush_tiles < 1) use_fp = false;
     }
     return DS_OK;
