@@ -42,8 +42,10 @@ struct GemmParams {
     int bk;           // k values per tile = kt_words * num
     int ntiles;       // ceil(row_len / kt_words)
     int flush_tiles;  // FP path: tiles between drains of the float accumulators
+    int tail_neg;     // FP path: tail slots of a row (k >= K) that decode as a negative weight
     // convolution geometry (CONV only)
     int C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW, P;  // P = OH*OW
+    unsigned magic_khw, magic_kw;  // ceil(2^32 / d): __umulhi(k, magic) == k / d for the k used here
     // fused prologue / epilogue
     int in_kind, out_kind, relu, requant;
     Quant q;
@@ -52,7 +54,7 @@ struct GemmParams {
 };
 
 struct KEntry {
-    int off;  // ic*H*W + kh*W + kw
+    int off;  // byte offset (ic*H*W + kh*W + kw) * 4
     int kh;   // 31 marks k >= K (bit 31 of a row mask is never set)
     int kw;
     int pad;
@@ -113,7 +115,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
     const int a_k = CONV ? (t / BM) : (t % KL);
 
     const int32_t* xi = static_cast<const int32_t*>(p.x);
-    long long x_base = 0;  // CONV: element offset of (b, 0, ih0, iw0); LINEAR: of (m0 + a_m, a_k)
+    long long x_base = 0;   // LINEAR: element offset of (m0 + a_m, a_k)
+    unsigned x_boff = 0;    // CONV: byte offset of (b, 0, ih0, iw0) modulo 2^32 (tensor < 4 GiB)
     uint32_t rowmask = 0, colmask = 0;  // CONV: valid kh / kw; LINEAR: rowmask bit e = row valid
     if (CONV) {
         const int m = m0 + a_m;
@@ -125,7 +128,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
                 if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask |= 1u << kh;
             for (int kw = 0; kw < p.KW; ++kw)
                 if (unsigned(iw0 + kw) < unsigned(p.W)) colmask |= 1u << kw;
-            x_base = (long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0;
+            x_boff = unsigned(((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4);
         }
     } else {
         x_base = (long long)(m0 + a_m) * p.K + a_k;
@@ -176,11 +179,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
             KEntry e;
             e.pad = 0;
             if (t < p.bk && k < p.K) {
-                const int khw = p.KH * p.KW;
-                const int ic = k / khw, tap = k - ic * khw;
-                e.kh = tap / p.KW;
+                // magic == 0 stands for a divisor of 1
+                const int ic = p.magic_khw ? int(__umulhi(unsigned(k), p.magic_khw)) : k;
+                const int tap = k - ic * (p.KH * p.KW);
+                e.kh = p.magic_kw ? int(__umulhi(unsigned(tap), p.magic_kw)) : tap;
                 e.kw = tap - e.kh * p.KW;
-                e.off = ic * p.H * p.W + e.kh * p.W + e.kw;
+                e.off = (ic * p.H * p.W + e.kh * p.W + e.kw) * 4;
             } else {
                 e.off = 0;
                 e.kh = 31;
@@ -202,7 +206,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
                 int v = padv;
                 if (kl < BKT) {
                     const int4 ke = *reinterpret_cast<const int4*>(&s.ktab[buf][kl]);
-                    if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u) v = __ldg(xi + (x_base + ke.x));
+                    if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u)
+                        v = __ldg(reinterpret_cast<const int*>(reinterpret_cast<const char*>(p.x) +
+                                                               size_t(x_boff + unsigned(ke.x))));
                 }
                 a_reg[e] = v;
             }
@@ -243,62 +249,52 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
         return FP ? (f + 0.5f) : __int_as_float(__float2int_rz(f));
     };
 
-    // Decode `NUM` fields of one word into column n of the weight tile.
-    auto decode_word = [&](auto num_tag, uint32_t w, int buf, int krow, int n, int klive) {
-        constexpr int NUM = decltype(num_tag)::value;
-        const uint32_t fmask = (1u << p.dec.fw) - 1u;
+    // Decode the fields of one word into column n of the weight tile.  Tail slots (k >= K) of
+    // the last word decode like any field; the matching x values are stored as 0 so they add
+    // nothing, and the epilogue takes their share out of the negative-weight count.
+    const uint32_t fmask = (1u << p.dec.fw) - 1u;
+    auto decode_word = [&](uint32_t w, int buf, int krow, int n) {
         int negs = 0;
-#pragma unroll
-        for (int i = 0; i < NUM; ++i) {
+#pragma unroll 2
+        for (int i = 0; i < p.dec.num; ++i) {
             const uint32_t f = w & fmask;
             w >>= p.dec.fw;
-            int v0 = s.lut0[f];
-            if (i >= klive) v0 = 0;  // k >= K: the tail slots of the last word
+            const int v0 = s.lut0[f];
             s.b[buf][krow + i][n] = __int_as_float(v0);
-            if (FP) {
-                negs += int(uint32_t(v0) >> 31);
-            } else {
-                int v1 = s.lut1[f];
-                if (i >= klive) v1 = 0;
-                s.bm[buf][krow + i][n] = v1;
-            }
+            if (FP) negs += int(uint32_t(v0) >> 31);
+            else s.bm[buf][krow + i][n] = s.lut1[f];
         }
         if (FP && negs) atomicAdd(&s.negc[n], negs);
     };
 
     // Convert and store the registers of tile `tile` into shared buffer `buf`.
     auto stash = [&](int tile, int buf) {
-#pragma unroll
-        for (int e = 0; e < A_ELEMS; ++e) {
-            const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
-            const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
-            if (kl < BKT) s.a[buf][kl][ml] = to_smem_value(a_reg[e]);
-        }
         const int k0 = tile * p.bk;
+        if (tile + 1 < p.ntiles) {
+#pragma unroll
+            for (int e = 0; e < A_ELEMS; ++e) {
+                const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
+                const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
+                if (kl < BKT) s.a[buf][kl][ml] = to_smem_value(a_reg[e]);
+            }
+        } else {  // last tile: x is 0 where k >= K (see decode_word)
+#pragma unroll
+            for (int e = 0; e < A_ELEMS; ++e) {
+                const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
+                const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
+                if (kl < BKT) s.a[buf][kl][ml] = (k0 + kl < p.K) ? to_smem_value(a_reg[e]) : 0.f;
+            }
+        }
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
             const int wi = t + e * kThreads;
-            if (wi < nwords) {
-                const int n = wi & (BN - 1), jw = wi / BN;
-                const int krow = jw * p.dec.num;
-                const int klive = p.K - (k0 + krow);  // fields below this index are real weights
-                const uint32_t w = w_reg[e];
-                switch (p.dec.num) {
-                    case 4: decode_word(std::integral_constant<int, 4>(), w, buf, krow, n, klive); break;
-                    case 5: decode_word(std::integral_constant<int, 5>(), w, buf, krow, n, klive); break;
-                    case 6: decode_word(std::integral_constant<int, 6>(), w, buf, krow, n, klive); break;
-                    case 8: decode_word(std::integral_constant<int, 8>(), w, buf, krow, n, klive); break;
-                    case 10: decode_word(std::integral_constant<int, 10>(), w, buf, krow, n, klive); break;
-                    default: decode_word(std::integral_constant<int, 16>(), w, buf, krow, n, klive); break;
-                }
-            }
+            if (wi < nwords) decode_word(w_reg[e], buf, (wi / BN) * p.dec.num, wi & (BN - 1));
         }
     };
 
     auto compute = [&](int buf) {
-#pragma unroll
-        for (int k = 0; k < BKT; ++k) {
-            if (k >= p.bk) break;
+#pragma unroll 2
+        for (int k = 0; k < p.bk; ++k) {  // bk is even
             float a[kTM];
             *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[buf][k][4 * tm]);
             *reinterpret_cast<float4*>(&a[4]) =
@@ -383,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
         int c = 0;
         if (n < p.N) {
             if (p.bias) c = __ldg(p.bias + n);
-            if (FP) c += s.negc[ncol(j)];
+            if (FP) c += s.negc[ncol(j)] - p.tail_neg;
         }
         addc[j] = c;
     }
@@ -488,6 +484,15 @@ int launch_cfg(GemmParams& p, cudaStream_t st)
     if (p.kt_words < 1) return DS_ERR_UNSUPPORTED;
     p.bk = p.kt_words * p.dec.num;
     p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
+    if (p.bk & 1) {  // the k loop runs two columns per iteration
+        if (p.kt_words < 2) return DS_ERR_UNSUPPORTED;
+        p.kt_words -= 1;
+        p.bk = p.kt_words * p.dec.num;
+        if (p.bk & 1) return DS_ERR_UNSUPPORTED;
+        p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
+    }
+    // Every slot from K to the end of the last tile decodes from a zero field, i.e. as -2^0.
+    p.tail_neg = p.ntiles * p.bk - p.K;
     auto kern = gemm_kernel<TMG, TNG, TN, BKT, FP, CONV>;
     const size_t smem = sizeof(S);
     static bool attr_done = false;  // per instantiation
@@ -608,11 +613,16 @@ extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t*
     const int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
     const long long M = (long long)B * OH * OW, Kll = (long long)C * KH * KW;
     if (M > 2147483647LL || Kll > 2147483647LL || (long long)C * H * W > 2147483647LL) return DS_ERR_RANGE;
+    if ((long long)B * C * H * W * 4 >= (1ll << 32)) return DS_ERR_RANGE;   // 32-bit byte offsets into x
+    if (Kll * KH * KW >= (1ll << 32)) return DS_ERR_RANGE;                  // exactness of the magic division
     GemmParams p = {};
     p.x = x; p.packed = packed; p.bias = bias; p.out = out;
     p.M = int(M); p.K = int(Kll); p.N = OC;
     p.C = C; p.H = H; p.W = W; p.OC = OC; p.KH = KH; p.KW = KW;
     p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.OH = OH; p.OW = OW; p.P = OH * OW;
+    auto magic = [](int d) -> unsigned { return d == 1 ? 0u : unsigned(((1ull << 32) + unsigned(d) - 1) / unsigned(d)); };
+    p.magic_khw = magic(KH * KW);
+    p.magic_kw = magic(KW);
     bool fp = false;
     rc = setup_common(p, bits, base, fuse, fp);
     if (rc) return rc;
