@@ -5,20 +5,30 @@
 // One tiled kernel serves both the linear layer (x is [M,K] row-major) and the convolution
 // (x is unpadded NCHW; row m = (b,oh,ow), column k = (ic,kh,kw) is gathered on the fly, zero
 // padding by predication -- the im2col matrix never exists).  Packed weight words are
-// fetched from global memory and decoded once per CTA into shared memory; the decoded
-// sign/shift never goes back to HBM.
+// fetched from global memory and decoded once per CTA into shared memory through a small
+// lookup table; the decoded sign/shift never goes back to HBM.
 //
 // Two arithmetic paths, both bit-exact:
-//   * integer path (FP == false): acc += (x >> sh) * mul, a funnel shift on the integer ALU
-//     pipe plus an integer multiply-add on the FMA pipe.  Valid for every int32 input and
-//     wraps modulo 2^32 like the reference.
-//   * FP32-pipe path (FP == true): one FFMA with round-toward-minus-infinity per term.
-//     With xh = x + 0.5 and w = +-2^-r, floor(xh * w) equals (x >> r) for w > 0 and
-//     -(x >> r) - 1 for w < 0, because xh * w is never an integer.  Adding into an
-//     accumulator of the form 1.5*2^23 + A (A an integer, |A| < 2^22) makes the FMA's single
-//     rounding that floor.  The "-1" of every negative weight is a per-output constant that
-//     the epilogue adds back, and the accumulator is drained into an int32 register often
-//     enough that |A| stays below 2^22.  Needs base == 0 and a bound on |x| (act_bits).
+//   * integer path (MODE_INT): acc += (x >> sh) * mul, a funnel shift on the integer ALU pipe
+//     plus an integer multiply-add.  Valid for every int32 input, any base <= 0, and wraps
+//     modulo 2^32 like the reference.  256 threads, 8x8 outputs per thread in registers.
+//   * FP32-pipe path (MODE_FP): one FFMA with round-toward-minus-infinity per term.  With
+//     xh = x + 0.5 and w = +-2^-r, floor(xh * w) equals (x >> r) for w > 0 and -(x >> r) - 1
+//     for w < 0, because xh * w is never an integer.  Adding into an accumulator of the form
+//     1.5*2^23 + A (A an integer, |A| < 2^22) makes the FMA's single rounding exactly that
+//     floor.  The "-1" of every negative weight is a per-output constant that the epilogue
+//     adds back.  Before |A| can reach 2^22 the accumulators are drained into per-thread
+//     int32 slots in shared memory (red.shared.add), so registers hold only the float
+//     accumulators.  Needs base == 0 and a bound on |x| (act_bits).  512 threads, one CTA per
+//     SM, 256 output rows per CTA.
+//
+// Staging of x (template parameter AM):
+//   AM_LINEAR    x is [M,K]; a warp reads runs of consecutive k.
+//   AM_TABLE     convolution, any window: a per-tile table maps k -> (offset, kh, kw).
+//   AM_ROW + KW  convolution with a KW-wide window and a k-tile made of whole (ic,kh) rows:
+//                one table entry and one validity test per row, KW loads at constant
+//                offsets.  This is the cheap path used by 1x1, 3x3, 5x5 and 7x7 windows.
+#include <cstddef>
 #include <type_traits>
 
 #include "ds_common.cuh"
@@ -26,9 +36,10 @@
 namespace ds {
 namespace {
 
-constexpr int kThreads = 256;
 constexpr int kTM = 8;  // rows of x per thread
 constexpr int kPadMarker = 0x7FC0DEAD;  // NaN pattern standing for "integer 0, do not quantise"
+constexpr int MODE_INT = 0, MODE_FP = 1;
+constexpr int AM_LINEAR = -1, AM_TABLE = 0;  // AM >= 1: row mode with KW = AM
 
 struct GemmParams {
     const void* x;        // int32 or fp32
@@ -42,10 +53,11 @@ struct GemmParams {
     int bk;           // k values per tile = kt_words * num
     int ntiles;       // ceil(row_len / kt_words)
     int flush_tiles;  // FP path: tiles between drains of the float accumulators
-    int tail_neg;     // FP path: tail slots of a row (k >= K) that decode as a negative weight
-    // convolution geometry (CONV only)
+    int tail_neg;     // FP path: slots k >= K inside the last tile; each decodes as a negative weight
+    // convolution geometry
     int C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW, P;  // P = OH*OW
-    unsigned magic_khw, magic_kw;  // ceil(2^32 / d): __umulhi(k, magic) == k / d for the k used here
+    unsigned magic_khw, magic_kw, magic_kh;  // ceil(2^32 / d), 0 for d == 1: __umulhi(k, magic) == k / d
+    int rows_per_tile;  // row mode: (ic,kh) rows per k-tile = bk / KW
     // fused prologue / epilogue
     int in_kind, out_kind, relu, requant;
     Quant q;
@@ -53,43 +65,54 @@ struct GemmParams {
     float inv_scale;  // 2^-F
 };
 
-struct KEntry {
-    int off;  // byte offset (ic*H*W + kh*W + kw) * 4
-    int kh;   // 31 marks k >= K (bit 31 of a row mask is never set)
+struct alignas(16) KEntry {
+    int off;  // byte offset of the tap (table mode) or of the row start (row mode)
+    int kh;   // 31 marks an entry past the end of K (bit 31 of a row mask is never set)
     int kw;
     int pad;
 };
 
-template <int TMG, int TNG, int TN, int BKT, bool FP>
+template <int NT, int TMG, int TNG, int TN, int BKT, int MODE>
 struct Smem {
+    static constexpr bool FP = MODE == MODE_FP;
     static constexpr int BM = TMG * kTM;
     static constexpr int BN = TNG * TN;
     static constexpr int AP = BM + 4;
-    float a[2][BKT][AP];  // FP: x + 0.5 as float; integer path: x (int bits)
-    float b[2][BKT][BN];  // FP: +-2^-r; integer path: shift amounts (int bits)
-    int bm[FP ? 1 : 2][FP ? 1 : BKT][FP ? 1 : BN];  // integer path: multipliers
-    KEntry ktab[2][BKT];
-    int lut0[256];             // decoded weight per field value: FP float bits / integer shift
-    int lut1[FP ? 1 : 256];    // integer path: multiplier
-    int negc[BN];              // FP: negative weights per output column
-    int accs[FP ? kTM * TN * kThreads : 1];  // FP: drained accumulators, [slot][thread]
+    // Every member that is read with 8- or 16-byte loads sits at a multiple of 16 bytes.
+    alignas(16) float a[2][BKT][AP];  // FP: x + 0.5 as float; integer path: x (int bits)
+    alignas(16) float b[2][BKT][BN];  // FP: +-2^-r; integer path: shift amounts (int bits)
+    alignas(16) KEntry ktab[2][BKT];
+    alignas(16) int bm[FP ? 1 : 2][FP ? 1 : BKT][FP ? 1 : BN];  // integer path: multipliers
+    int lut0[256];           // decoded weight per field value: FP float bits / integer shift
+    int lut1[FP ? 1 : 256];  // integer path: multiplier
+    int negc[BN];            // FP: negative weights per output column
+    int accs[FP ? kTM * TN * NT : 1];  // FP: drained accumulators, [slot][thread]
 };
 
 __device__ __forceinline__ void red_shared_add(int* addr, int v)
 {
-    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(addr)), "r"(v) : "memory");
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(addr)), "r"(v)
+                 : "memory");
 }
 
+__device__ __forceinline__ int magic_div(int k, unsigned magic) { return magic ? int(__umulhi(unsigned(k), magic)) : k; }
+
 // ---------------------------------------------------------------------------------------------
-template <int TMG, int TNG, int TN, int BKT, bool FP, bool CONV>
-__global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
+template <int NT, int TMG, int TNG, int TN, int BKT, int MODE, int AM>
+__global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const GemmParams p)
 {
-    using S = Smem<TMG, TNG, TN, BKT, FP>;
+    using S = Smem<NT, TMG, TNG, TN, BKT, MODE>;
+    constexpr bool FP = MODE == MODE_FP;
+    constexpr bool CONV = AM != AM_LINEAR;
+    constexpr bool ROW = AM >= 1;
+    constexpr int KW = ROW ? AM : 1;
     constexpr int BM = S::BM, BN = S::BN;
-    constexpr int EW = (BN * (BKT / 4) + kThreads - 1) / kThreads;  // words per thread (num >= 4)
-    static_assert(TMG * TNG == kThreads, "256 threads");
+    constexpr int EW = (BN * (BKT / 4) + NT - 1) / NT;  // words per thread (num >= 4)
+    static_assert(TMG * TNG == NT, "thread grid");
     static_assert(TN == 4 || TN == 8, "TN");
     static_assert((BN & (BN - 1)) == 0, "BN power of two");
+    static_assert(TMG % 8 == 0 && TNG % 8 == 0, "warp footprint");
+    static_assert(offsetof(S, ktab) % 16 == 0 && offsetof(S, b) % 16 == 0 && offsetof(S, bm) % 16 == 0, "alignment");
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     S& s = *reinterpret_cast<S*>(smem_raw);
@@ -97,20 +120,34 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
     const int t = threadIdx.x;
     const int m0 = blockIdx.x * BM;
     const int n0 = blockIdx.y * BN;
-    // Threads that share n are adjacent in m for the convolution (NCHW output is contiguous in
-    // m), and the other way round for the linear layer ([M,N] output is contiguous in n).
-    const int tm = CONV ? (t % TMG) : (t / TNG);
-    const int tn = CONV ? (t / TMG) : (t % TNG);
+    // A warp covers 8 x 4 thread tiles: 8 along the direction in which the output is contiguous
+    // (m for the NCHW convolution output, n for the [M,N] linear output), so that both operand
+    // fragments come from few shared-memory wavefronts and stores fill whole sectors.
+    const int lane = t & 31, warp = t >> 5;
+    int tm, tn;
+    if (CONV) {
+        constexpr int WMG = TMG / 8;
+        tm = (warp % WMG) * 8 + (lane & 7);
+        tn = (warp / WMG) * 4 + (lane >> 3);
+    } else {
+        constexpr int WNG = TNG / 8;
+        tn = (warp % WNG) * 8 + (lane & 7);
+        tm = (warp / WNG) * 4 + (lane >> 3);
+    }
 
     // ---- per-thread staging geometry -------------------------------------------------------
-    // CONV: one row m_local = t % BM, columns k_local = t / BM + (256 / BM) * e.
-    // LINEAR: one column k_local = t % KL, rows m_local = t / KL + (256 / KL) * e, KL = 32 or 16
+    // CONV: one row m_local = t % BM of the tile; `a_k` = t / BM picks every (NT / BM)-th column
+    //       (table mode) or (ic,kh) row (row mode) of the k-tile.
+    // LINEAR: one column k_local = t % KL, rows m_local = t / KL + (NT / KL) * e, KL = 32 or 16
     //         (k is contiguous in x, so a warp reads whole sectors).
     constexpr int KL = (BKT > 16) ? 32 : 16;
-    constexpr int A_MSTEP = kThreads / KL;
-    constexpr int A_KSTEP = (kThreads >= BM) ? kThreads / BM : 1;
-    constexpr int A_ELEMS = CONV ? (BKT + A_KSTEP - 1) / A_KSTEP : BM / A_MSTEP;
+    constexpr int A_MSTEP = NT / KL;
+    constexpr int A_KSTEP = (NT >= BM) ? NT / BM : 1;
+    // row mode: a k-tile holds a multiple of A_KSTEP rows; UNITS rows per thread per tile
+    constexpr int UNITS = (BKT / (KW * A_KSTEP)) > 0 ? (BKT / (KW * A_KSTEP)) : 1;
+    constexpr int A_ELEMS = ROW ? UNITS * KW : (CONV ? (BKT + A_KSTEP - 1) / A_KSTEP : (BM + A_MSTEP - 1) / A_MSTEP);
     static_assert(A_ELEMS <= 16, "staging registers");
+    static_assert(!CONV || NT >= BM, "one staging thread per row");
     const int a_m = CONV ? (t % BM) : (t / KL);
     const int a_k = CONV ? (t / BM) : (t % KL);
 
@@ -134,12 +171,12 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
         x_base = (long long)(m0 + a_m) * p.K + a_k;
 #pragma unroll
         for (int e = 0; e < A_ELEMS; ++e)
-            if (m0 + a_m + e * A_MSTEP < p.M) rowmask |= 1u << e;
+            if (a_m + e * A_MSTEP < BM && m0 + a_m + e * A_MSTEP < p.M) rowmask |= 1u << e;
         if (a_k >= p.bk) rowmask = 0;
     }
 
     // ---- decode table, accumulators ------------------------------------------------------------
-    for (int f = t; f < (1 << p.dec.fw); f += kThreads) {
+    for (int f = t; f < (1 << p.dec.fw); f += NT) {
         if (FP) {
             int neg;
             s.lut0[f] = __float_as_int(decode_f32(uint32_t(f), p.dec, true, neg));
@@ -158,9 +195,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
                 accf[i][j] = kMagic;
-                s.accs[(i * TN + j) * kThreads + t] = 0;
+                s.accs[(i * TN + j) * NT + t] = 0;
             }
-        for (int i = t; i < BN; i += kThreads) s.negc[i] = 0;
+        for (int i = t; i < BN; i += NT) s.negc[i] = 0;
     } else {
 #pragma unroll
         for (int i = 0; i < kTM; ++i)
@@ -174,24 +211,30 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
     const int nwords = BN * p.kt_words;
 
     auto fill_ktab = [&](int tile, int buf) {
-        if (CONV && t < BKT) {
+        if (!CONV || t >= BKT) return;
+        KEntry e;
+        e.pad = 0;
+        e.off = 0;
+        e.kh = 31;
+        e.kw = 0;
+        if (ROW) {
+            const int row = tile * p.rows_per_tile + t;  // global (ic,kh) row index
+            if (t < p.rows_per_tile && row < p.C * p.KH) {
+                const int ic = magic_div(row, p.magic_kh);
+                e.kh = row - ic * p.KH;
+                e.off = (ic * p.H * p.W + e.kh * p.W) * 4;
+            }
+        } else {
             const int k = tile * p.bk + t;
-            KEntry e;
-            e.pad = 0;
             if (t < p.bk && k < p.K) {
-                // magic == 0 stands for a divisor of 1
-                const int ic = p.magic_khw ? int(__umulhi(unsigned(k), p.magic_khw)) : k;
+                const int ic = magic_div(k, p.magic_khw);
                 const int tap = k - ic * (p.KH * p.KW);
-                e.kh = p.magic_kw ? int(__umulhi(unsigned(tap), p.magic_kw)) : tap;
+                e.kh = magic_div(tap, p.magic_kw);
                 e.kw = tap - e.kh * p.KW;
                 e.off = (ic * p.H * p.W + e.kh * p.W + e.kw) * 4;
-            } else {
-                e.off = 0;
-                e.kh = 31;
-                e.kw = 0;
             }
-            s.ktab[buf][t] = e;
         }
+        s.ktab[buf][t] = e;
     };
 
     // Raw fetch of tile `tile` into registers.  fp32 inputs keep their bits; positions outside
@@ -199,7 +242,23 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
     // without quantising it.
     auto fetch = [&](int tile, int buf) {
         const int padv = (p.in_kind == DS_IN_I32) ? 0 : kPadMarker;
-        if (CONV) {
+        const char* xb = reinterpret_cast<const char*>(p.x);
+        if (ROW) {
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                const int r = a_k + u * A_KSTEP;
+                const int2 e = *reinterpret_cast<const int2*>(&s.ktab[buf][r < BKT ? r : 0]);
+                const bool rv = (r < BKT) && ((rowmask >> e.y) & 1u);
+                const unsigned base = x_boff + unsigned(e.x);
+#pragma unroll
+                for (int kw = 0; kw < KW; ++kw) {
+                    int v = padv;
+                    if (rv && (colmask & (1u << kw)))
+                        v = __ldg(reinterpret_cast<const int*>(xb + size_t(base + 4u * kw)));
+                    a_reg[u * KW + kw] = v;
+                }
+            }
+        } else if (CONV) {
 #pragma unroll
             for (int e = 0; e < A_ELEMS; ++e) {
                 const int kl = a_k + e * A_KSTEP;
@@ -207,8 +266,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
                 if (kl < BKT) {
                     const int4 ke = *reinterpret_cast<const int4*>(&s.ktab[buf][kl]);
                     if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u)
-                        v = __ldg(reinterpret_cast<const int*>(reinterpret_cast<const char*>(p.x) +
-                                                               size_t(x_boff + unsigned(ke.x))));
+                        v = __ldg(reinterpret_cast<const int*>(xb + size_t(x_boff + unsigned(ke.x))));
                 }
                 a_reg[e] = v;
             }
@@ -225,7 +283,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
         const int w0 = tile * p.kt_words;
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
-            const int wi = t + e * kThreads;
+            const int wi = t + e * NT;
             uint32_t w = 0;
             if (wi < nwords) {
                 const int n = wi & (BN - 1), jw = wi / BN;
@@ -267,34 +325,47 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
         if (FP && negs) atomicAdd(&s.negc[n], negs);
     };
 
-    // Convert and store the registers of tile `tile` into shared buffer `buf`.
+    // Convert and store the registers of tile `tile` into shared buffer `buf`.  In the last
+    // tile x is stored as 0 where k >= K (see decode_word).
     auto stash = [&](int tile, int buf) {
         const int k0 = tile * p.bk;
-        if (tile + 1 < p.ntiles) {
+        const bool last = tile + 1 >= p.ntiles;
+        if (ROW) {
 #pragma unroll
-            for (int e = 0; e < A_ELEMS; ++e) {
-                const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
-                const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
-                if (kl < BKT) s.a[buf][kl][ml] = to_smem_value(a_reg[e]);
+            for (int u = 0; u < UNITS; ++u) {
+                const int r = a_k + u * A_KSTEP;
+                if (r * KW + KW <= BKT) {  // always true for the rows a k-tile can hold
+#pragma unroll
+                    for (int kw = 0; kw < KW; ++kw) {
+                        const int kl = r * KW + kw;
+                        float o = to_smem_value(a_reg[u * KW + kw]);
+                        if (last && k0 + kl >= p.K) o = 0.f;
+                        s.a[buf][kl][a_m] = o;
+                    }
+                }
             }
-        } else {  // last tile: x is 0 where k >= K (see decode_word)
+        } else {
 #pragma unroll
             for (int e = 0; e < A_ELEMS; ++e) {
                 const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
                 const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
-                if (kl < BKT) s.a[buf][kl][ml] = (k0 + kl < p.K) ? to_smem_value(a_reg[e]) : 0.f;
+                if (kl < BKT && ml < BM) {
+                    float o = to_smem_value(a_reg[e]);
+                    if (last && k0 + kl >= p.K) o = 0.f;
+                    s.a[buf][kl][ml] = o;
+                }
             }
         }
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
-            const int wi = t + e * kThreads;
+            const int wi = t + e * NT;
             if (wi < nwords) decode_word(w_reg[e], buf, (wi / BN) * p.dec.num, wi & (BN - 1));
         }
     };
 
     auto compute = [&](int buf) {
-#pragma unroll 2
-        for (int k = 0; k < p.bk; ++k) {  // bk is even
+#pragma unroll 4
+        for (int k = 0; k < p.bk; ++k) {
             float a[kTM];
             *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[buf][k][4 * tm]);
             *reinterpret_cast<float4*>(&a[4]) =
@@ -332,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
         for (int i = 0; i < kTM; ++i)
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
-                red_shared_add(&s.accs[(i * TN + j) * kThreads + t], __float_as_int(accf[i][j]));
+                red_shared_add(&s.accs[(i * TN + j) * NT + t], __float_as_int(accf[i][j]));
                 accf[i][j] = kMagic;
             }
         ++ndrains;
@@ -368,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
     auto ncol = [&](int j) { return (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j); };
     auto mrow = [&](int i) { return (i >= 4) ? (BM / 2 + 4 * tm + i - 4) : (4 * tm + i); };
     auto accv = [&](int i, int j) -> int {
-        if (FP) return s.accs[(i * TN + j) * kThreads + t] - ndrains * kMagicBits;
+        if (FP) return s.accs[(i * TN + j) * NT + t] - ndrains * kMagicBits;
         return acc[FP ? 0 : i][FP ? 0 : j];
     };
 
@@ -475,25 +546,40 @@ __global__ void __launch_bounds__(kThreads, 2) gemm_kernel(const GemmParams p)
 }
 
 // ---------------------------------------------------------------------------------------------
-template <int TMG, int TNG, int TN, int BKT, bool FP, bool CONV>
-int launch_cfg(GemmParams& p, cudaStream_t st)
+// Chooses the k-tile: `bk` values of k per tile, a multiple of num (whole packed words) and, in
+// row mode, of A_KSTEP*KW (whole rows, split evenly over the staging threads of one x row).
+template <int BKT, int AM, int A_KSTEP>
+bool choose_tile(GemmParams& p)
 {
-    using S = Smem<TMG, TNG, TN, BKT, FP>;
-    constexpr int BM = S::BM, BN = S::BN;
-    p.kt_words = BKT / p.dec.num;
-    if (p.kt_words < 1) return DS_ERR_UNSUPPORTED;
-    p.bk = p.kt_words * p.dec.num;
-    p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
-    if (p.bk & 1) {  // the k loop runs two columns per iteration
-        if (p.kt_words < 2) return DS_ERR_UNSUPPORTED;
-        p.kt_words -= 1;
-        p.bk = p.kt_words * p.dec.num;
-        if (p.bk & 1) return DS_ERR_UNSUPPORTED;
-        p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
+    constexpr int KW = AM >= 1 ? AM : 1;
+    int best = 0;
+    for (int bk = BKT; bk >= 2 && !best; --bk) {
+        if (bk % p.dec.num) continue;
+        if (AM >= 1 && bk % (A_KSTEP * KW)) continue;
+        best = bk;
     }
+    if (!best) return false;
+    p.bk = best;
+    p.kt_words = best / p.dec.num;
+    p.rows_per_tile = best / KW;
+    p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
     // Every slot from K to the end of the last tile decodes from a zero field, i.e. as -2^0.
     p.tail_neg = p.ntiles * p.bk - p.K;
-    auto kern = gemm_kernel<TMG, TNG, TN, BKT, FP, CONV>;
+    return true;
+}
+
+template <int NT, int TMG, int TNG, int TN, int BKT, int MODE, int AM>
+int launch_cfg(GemmParams p, cudaStream_t st)
+{
+    using S = Smem<NT, TMG, TNG, TN, BKT, MODE>;
+    constexpr int BM = S::BM, BN = S::BN;
+    if (!choose_tile<BKT, AM, (NT >= BM ? NT / BM : 1)>(p)) return DS_ERR_UNSUPPORTED;
+    if (MODE == MODE_FP) {
+        p.flush_tiles /= p.bk;  // setup_common left the number of terms that cannot overflow
+        if (p.flush_tiles < 1) return DS_ERR_UNSUPPORTED;
+        if (p.flush_tiles > 4096) p.flush_tiles = 4096;
+    }
+    auto kern = gemm_kernel<NT, TMG, TNG, TN, BKT, MODE, AM>;
     const size_t smem = sizeof(S);
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
@@ -505,19 +591,36 @@ int launch_cfg(GemmParams& p, cudaStream_t st)
     }
     const long long gx = ((long long)p.M + BM - 1) / BM, gy = (p.N + BN - 1) / BN;
     if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
-    kern<<<dim3((unsigned)gx, (unsigned)gy), kThreads, smem, st>>>(p);
+    kern<<<dim3((unsigned)gx, (unsigned)gy), NT, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
-template <bool FP, bool CONV>
-int launch_path(GemmParams& p, cudaStream_t st)
+// Tile shape by output width.  FP path: 256 rows x 128 or 64 columns, 512 threads.
+// Integer path: 128 x 128, 256 x 64 or 256 x 32, 256 threads.
+template <int AM>
+int launch_am(const GemmParams& p, bool fp, cudaStream_t st)
 {
-    // Tile shape by output width: 128x128 for wide layers, 256x64 for 64-channel layers,
-    // 256x32 below that; 64x128 when there are few rows (small-batch linear layers).
-    if (!CONV && p.M <= 64) return launch_cfg<8, 32, 4, 20, FP, CONV>(p, st);
-    if (p.N > 64) return launch_cfg<16, 16, 8, 20, FP, CONV>(p, st);
-    if (p.N > 32) return launch_cfg<32, 8, 8, 16, FP, CONV>(p, st);
-    return launch_cfg<32, 8, 4, 16, FP, CONV>(p, st);
+    if (fp) {
+        if (p.N > 64) return launch_cfg<512, 32, 16, 8, 28, MODE_FP, AM>(p, st);
+        return launch_cfg<512, 32, 16, 4, 28, MODE_FP, AM>(p, st);
+    }
+    if (p.N > 64) return launch_cfg<256, 16, 16, 8, 20, MODE_INT, AM>(p, st);
+    if (p.N > 32) return launch_cfg<256, 32, 8, 8, 16, MODE_INT, AM>(p, st);
+    return launch_cfg<256, 32, 8, 4, 16, MODE_INT, AM>(p, st);
+}
+
+int launch_conv(const GemmParams& p, bool fp, cudaStream_t st)
+{
+    int rc = DS_ERR_UNSUPPORTED;
+    switch (p.KW) {  // row mode where the window width has an instantiation and a k-tile exists
+        case 1: rc = launch_am<1>(p, fp, st); break;
+        case 3: rc = launch_am<3>(p, fp, st); break;
+        case 5: rc = launch_am<5>(p, fp, st); break;
+        case 7: rc = launch_am<7>(p, fp, st); break;
+        default: break;
+    }
+    if (rc == DS_ERR_UNSUPPORTED) rc = launch_am<AM_TABLE>(p, fp, st);
+    return rc;
 }
 
 int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool& use_fp)
@@ -553,17 +656,18 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.rq_lo = int(lo);
         p.rq_hi = int(hi);
     }
-    // FP32-pipe path: needs base == 0 and every |x| <= 2^(act_bits-1) <= 2^19, and at least
-    // one k-tile (<= 20 terms of magnitude <= 2^(act_bits-1) + 1) between drains.
+    // FP32-pipe path: needs base == 0, every |x| <= 2^(act_bits-1) <= 2^17, and room for at
+    // least one k-tile of terms (each of magnitude <= 2^(act_bits-1) + 1) between drains.
     int ab = f.act_bits;
     if (f.in_kind == DS_IN_F32_CONV) ab = p.q.sign_mode ? F + 2 : I + F;
     if (f.in_kind == DS_IN_F32_LINEAR) ab = 0;
     use_fp = (base == 0 && ab >= 1 && ab <= 18);
+    p.flush_tiles = 0;
     if (use_fp) {
         const long long per_term = (1ll << (ab - 1)) + 1;
         const long long terms = ((1ll << 22) - 1) / per_term;  // terms that cannot overflow
-        p.flush_tiles = int(terms / 20 > 1024 ? 1024 : terms / 20);  // tiles of <= 20 terms
-        if (p.flush_tiles < 1) use_fp = false;
+        p.flush_tiles = int(terms > (1 << 20) ? (1 << 20) : terms);  // divided by bk at launch
+        if (terms < 28) use_fp = false;
     }
     return DS_OK;
 }
@@ -574,6 +678,8 @@ int check_ptrs(const void* x, const void* packed, const void* out)
     if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return DS_ERR_ALIGN;
     return DS_OK;
 }
+
+unsigned magic_of(int d) { return d == 1 ? 0u : unsigned(((1ull << 32) + unsigned(d) - 1) / unsigned(d)); }
 
 }  // namespace
 }  // namespace ds
@@ -594,8 +700,7 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     rc = setup_common(p, bits, base, fuse, fp);
     if (rc) return rc;
     if (p.residual && (reinterpret_cast<uintptr_t>(p.residual) & 3u)) return DS_ERR_ALIGN;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return fp ? launch_path<true, false>(p, st) : launch_path<false, false>(p, st);
+    return launch_am<AM_LINEAR>(p, fp, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t* bias, void* out, int B,
@@ -613,21 +718,20 @@ extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t*
     const int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
     const long long M = (long long)B * OH * OW, Kll = (long long)C * KH * KW;
     if (M > 2147483647LL || Kll > 2147483647LL || (long long)C * H * W > 2147483647LL) return DS_ERR_RANGE;
-    if ((long long)B * C * H * W * 4 >= (1ll << 32)) return DS_ERR_RANGE;   // 32-bit byte offsets into x
-    if (Kll * KH * KW >= (1ll << 32)) return DS_ERR_RANGE;                  // exactness of the magic division
+    if ((long long)B * C * H * W * 4 >= (1ll << 32)) return DS_ERR_RANGE;  // 32-bit byte offsets into x
+    if (Kll * KH * KW >= (1ll << 32)) return DS_ERR_RANGE;                 // exactness of the magic division
     GemmParams p = {};
     p.x = x; p.packed = packed; p.bias = bias; p.out = out;
     p.M = int(M); p.K = int(Kll); p.N = OC;
     p.C = C; p.H = H; p.W = W; p.OC = OC; p.KH = KH; p.KW = KW;
     p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.OH = OH; p.OW = OW; p.P = OH * OW;
-    auto magic = [](int d) -> unsigned { return d == 1 ? 0u : unsigned(((1ull << 32) + unsigned(d) - 1) / unsigned(d)); };
-    p.magic_khw = magic(KH * KW);
-    p.magic_kw = magic(KW);
+    p.magic_khw = magic_of(KH * KW);
+    p.magic_kw = magic_of(KW);
+    p.magic_kh = magic_of(KH);
     bool fp = false;
     rc = setup_common(p, bits, base, fuse, fp);
     if (rc) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return fp ? launch_path<true, true>(p, st) : launch_path<false, true>(p, st);
+    return launch_conv(p, fp, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ds_linear_i32(const int32_t* x, const int32_t* packed, const int32_t* bias, int32_t* out,

@@ -125,6 +125,8 @@ int ds_quantize_f32(const float *x, int32_t *out, long long n, int kind, int act
  *   mode 0: shift + add (both on the integer ALU pipe)
  *   mode 1: shift + integer multiply-add (ALU pipe + FMA pipe)
  *   mode 2: FP32 fused multiply-add with round-down (FMA pipe)
+ *   mode 3: packed FP32 pair fused multiply-add with round-down (fma.rm.f32x2, two terms each)
+ *   mode 4: mode 3 with one independent integer instruction issued beside every packed FMA
  * Runs on `stream`, synchronises, and writes the sustained rate in shift-accumulate
  * operations per second (one op = one shift plus one signed accumulate) to *ops_per_s.
  */
