@@ -28,49 +28,10 @@
 //   AM_ROW + KW  convolution with a KW-wide window and a k-tile made of whole (ic,kh) rows:
 //                one table entry and one validity test per row, KW loads at constant
 //                offsets.  This is the cheap path used by 1x1, 3x3, 5x5 and 7x7 windows.
-#include <cstddef>
-#include <type_traits>
-
-#include "ds_common.cuh"
+#include "ds_gemm_common.cuh"
 
 namespace ds {
 namespace {
-
-constexpr int kTM = 8;  // rows of x per thread
-constexpr int kPadMarker = 0x7FC0DEAD;  // NaN pattern standing for "integer 0, do not quantise"
-constexpr int MODE_INT = 0, MODE_FP = 1;
-constexpr int AM_LINEAR = -1, AM_TABLE = 0;  // AM >= 1: row mode with KW = AM
-
-struct GemmParams {
-    const void* x;        // int32 or fp32
-    const int32_t* packed;
-    const int32_t* bias;  // may be null
-    void* out;            // int32 or fp32
-    const int32_t* residual;
-    int M, K, N;
-    Decode dec;
-    int kt_words;     // packed words per row per k-tile
-    int bk;           // k values per tile = kt_words * num
-    int ntiles;       // ceil(row_len / kt_words)
-    int flush_tiles;  // FP path: tiles between drains of the float accumulators
-    int tail_neg;     // FP path: slots k >= K inside the last tile; each decodes as a negative weight
-    // convolution geometry
-    int C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW, P;  // P = OH*OW
-    unsigned magic_khw, magic_kw, magic_kh;  // ceil(2^32 / d), 0 for d == 1: __umulhi(k, magic) == k / d
-    int rows_per_tile;  // row mode: (ic,kh) rows per k-tile = bk / KW
-    // fused prologue / epilogue
-    int in_kind, out_kind, relu, requant;
-    Quant q;
-    int rq_lo, rq_hi;
-    float inv_scale;  // 2^-F
-};
-
-struct alignas(16) KEntry {
-    int off;  // byte offset of the tap (table mode) or of the row start (row mode)
-    int kh;   // 31 marks an entry past the end of K (bit 31 of a row mask is never set)
-    int kw;
-    int pad;
-};
 
 template <int NT, int TMG, int TNG, int TN, int BKT, int MODE>
 struct Smem {
@@ -88,14 +49,6 @@ struct Smem {
     int negc[BN];            // FP: negative weights per output column
     int accs[FP ? kTM * TN * NT : 1];  // FP: drained accumulators, [slot][thread]
 };
-
-__device__ __forceinline__ void red_shared_add(int* addr, int v)
-{
-    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(addr)), "r"(v)
-                 : "memory");
-}
-
-__device__ __forceinline__ int magic_div(int k, unsigned magic) { return magic ? int(__umulhi(unsigned(k), magic)) : k; }
 
 // ---------------------------------------------------------------------------------------------
 template <int NT, int TMG, int TNG, int TN, int BKT, int MODE, int AM>
@@ -153,7 +106,8 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 
     const int32_t* xi = static_cast<const int32_t*>(p.x);
     long long x_base = 0;   // LINEAR: element offset of (m0 + a_m, a_k)
-    unsigned x_boff = 0;    // CONV: byte offset of (b, 0, ih0, iw0) modulo 2^32 (tensor < 4 GiB)
+    const char* x_pix = reinterpret_cast<const char*>(p.x);  // CONV: address of (b, 0, ih0, iw0); may lie
+                                                             // outside the tensor, only valid taps are read
     uint32_t rowmask = 0, colmask = 0;  // CONV: valid kh / kw; LINEAR: rowmask bit e = row valid
     if (CONV) {
         const int m = m0 + a_m;
@@ -165,7 +119,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
                 if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask |= 1u << kh;
             for (int kw = 0; kw < p.KW; ++kw)
                 if (unsigned(iw0 + kw) < unsigned(p.W)) colmask |= 1u << kw;
-            x_boff = unsigned(((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4);
+            x_pix += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4;
         }
     } else {
         x_base = (long long)(m0 + a_m) * p.K + a_k;
@@ -209,6 +163,16 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     int a_reg[A_ELEMS];
     uint32_t w_reg[EW];
     const int nwords = BN * p.kt_words;
+    // Word e of this thread: column n = wi % BN, word jw = wi / BN of the k-tile.
+    const int32_t* w_ptr[EW];  // address of word jw of tile 0, null if the thread has no such word
+    int w_jw[EW];
+#pragma unroll
+    for (int e = 0; e < EW; ++e) {
+        const int wi = t + e * NT;
+        const int n = wi & (BN - 1);
+        w_jw[e] = wi / BN;
+        w_ptr[e] = (wi < nwords && n0 + n < p.N) ? p.packed + (long long)(n0 + n) * p.dec.row_len + w_jw[e] : nullptr;
+    }
 
     auto fill_ktab = [&](int tile, int buf) {
         if (!CONV || t >= BKT) return;
@@ -242,19 +206,17 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     // without quantising it.
     auto fetch = [&](int tile, int buf) {
         const int padv = (p.in_kind == DS_IN_I32) ? 0 : kPadMarker;
-        const char* xb = reinterpret_cast<const char*>(p.x);
         if (ROW) {
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
-                const int r = a_k + u * A_KSTEP;
-                const int2 e = *reinterpret_cast<const int2*>(&s.ktab[buf][r < BKT ? r : 0]);
-                const bool rv = (r < BKT) && ((rowmask >> e.y) & 1u);
-                const unsigned base = x_boff + unsigned(e.x);
+                const int r = a_k + u * A_KSTEP;  // < BKT / KW by construction of UNITS
+                const int2 e = *reinterpret_cast<const int2*>(&s.ktab[buf][r]);
+                const bool rv = (rowmask >> e.y) & 1u;
+                const int* rowp = reinterpret_cast<const int*>(x_pix + e.x);
 #pragma unroll
                 for (int kw = 0; kw < KW; ++kw) {
                     int v = padv;
-                    if (rv && (colmask & (1u << kw)))
-                        v = __ldg(reinterpret_cast<const int*>(xb + size_t(base + 4u * kw)));
+                    if (rv && (colmask & (1u << kw))) v = __ldg(rowp + kw);
                     a_reg[u * KW + kw] = v;
                 }
             }
@@ -266,7 +228,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
                 if (kl < BKT) {
                     const int4 ke = *reinterpret_cast<const int4*>(&s.ktab[buf][kl]);
                     if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u)
-                        v = __ldg(reinterpret_cast<const int*>(xb + size_t(x_boff + unsigned(ke.x))));
+                        v = __ldg(reinterpret_cast<const int*>(x_pix + ke.x));
                 }
                 a_reg[e] = v;
             }
@@ -283,65 +245,27 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
         const int w0 = tile * p.kt_words;
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
-            const int wi = t + e * NT;
             uint32_t w = 0;
-            if (wi < nwords) {
-                const int n = wi & (BN - 1), jw = wi / BN;
-                if (n0 + n < p.N && w0 + jw < p.dec.row_len)
-                    w = uint32_t(__ldg(p.packed + (long long)(n0 + n) * p.dec.row_len + w0 + jw));
-            }
+            if (w_ptr[e] && w0 + w_jw[e] < p.dec.row_len) w = uint32_t(__ldg(w_ptr[e] + w0));
             w_reg[e] = w;
         }
     };
 
-    auto to_smem_value = [&](int v) -> float {
-        if (p.in_kind == DS_IN_I32) {
-            // x + 0.5 without an int->float conversion: adding 2x+1 to the bits of
-            // 1.5*2^22 (ulp 0.5) gives 1.5*2^22 + x + 0.5 exactly for |x| < 2^20.
-            return FP ? (__int_as_float(2 * v + (kHalfMagicBits + 1)) - kHalfMagic) : __int_as_float(v);
-        }
-        float f;  // the quantised value, an integer held in a float
-        if (v == kPadMarker) f = 0.f;
-        else if (p.in_kind == DS_IN_F32_CONV) f = quant_conv_f(__int_as_float(v), p.q);
-        else f = truncf(__int_as_float(v) * p.q.scale);
-        return FP ? (f + 0.5f) : __int_as_float(__float2int_rz(f));
-    };
-
-    // Decode the fields of one word into column n of the weight tile.  Tail slots (k >= K) of
-    // the last word decode like any field; the matching x values are stored as 0 so they add
-    // nothing, and the epilogue takes their share out of the negative-weight count.
-    const uint32_t fmask = (1u << p.dec.fw) - 1u;
-    auto decode_word = [&](uint32_t w, int buf, int krow, int n) {
-        int negs = 0;
-#pragma unroll 2
-        for (int i = 0; i < p.dec.num; ++i) {
-            const uint32_t f = w & fmask;
-            w >>= p.dec.fw;
-            const int v0 = s.lut0[f];
-            s.b[buf][krow + i][n] = __int_as_float(v0);
-            if (FP) negs += int(uint32_t(v0) >> 31);
-            else s.bm[buf][krow + i][n] = s.lut1[f];
-        }
-        if (FP && negs) atomicAdd(&s.negc[n], negs);
-    };
-
-    // Convert and store the registers of tile `tile` into shared buffer `buf`.  In the last
-    // tile x is stored as 0 where k >= K (see decode_word).
-    auto stash = [&](int tile, int buf) {
+    // Convert and store the x registers into shared buffer `buf`.  LAST: the tile may reach past
+    // K, where x is stored as 0 (see decode_word).
+    auto stash_a = [&](auto in32_tag, auto last_tag, int tile, int buf) {
+        constexpr bool LAST = decltype(last_tag)::value;
         const int k0 = tile * p.bk;
-        const bool last = tile + 1 >= p.ntiles;
         if (ROW) {
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
                 const int r = a_k + u * A_KSTEP;
-                if (r * KW + KW <= BKT) {  // always true for the rows a k-tile can hold
 #pragma unroll
-                    for (int kw = 0; kw < KW; ++kw) {
-                        const int kl = r * KW + kw;
-                        float o = to_smem_value(a_reg[u * KW + kw]);
-                        if (last && k0 + kl >= p.K) o = 0.f;
-                        s.a[buf][kl][a_m] = o;
-                    }
+                for (int kw = 0; kw < KW; ++kw) {
+                    const int kl = r * KW + kw;
+                    float o = operand_of<FP, decltype(in32_tag)::value>(p, a_reg[u * KW + kw]);
+                    if (LAST && k0 + kl >= p.K) o = 0.f;
+                    s.a[buf][kl][a_m] = o;
                 }
             }
         } else {
@@ -350,16 +274,56 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
                 const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
                 const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
                 if (kl < BKT && ml < BM) {
-                    float o = to_smem_value(a_reg[e]);
-                    if (last && k0 + kl >= p.K) o = 0.f;
+                    float o = operand_of<FP, decltype(in32_tag)::value>(p, a_reg[e]);
+                    if (LAST && k0 + kl >= p.K) o = 0.f;
                     s.a[buf][kl][ml] = o;
                 }
             }
         }
+    };
+
+    // Decode the NUM fields of each of this thread's words into the weight tile.  Tail slots
+    // (k >= K) of the last word decode like any field; the matching x values are stored as 0 so
+    // they add nothing, and the epilogue takes their share out of the negative-weight count.
+    const uint32_t fmask = (1u << p.dec.fw) - 1u;
+    auto decode_words = [&](auto num_tag, int buf) {
+        constexpr int NUM = decltype(num_tag)::value;
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
-            const int wi = t + e * NT;
-            if (wi < nwords) decode_word(w_reg[e], buf, (wi / BN) * p.dec.num, wi & (BN - 1));
+            if (!w_ptr[e]) continue;
+            const int n = (t + e * NT) & (BN - 1);
+            float* dst = &s.b[buf][w_jw[e] * NUM][n];
+            int* dstm = &s.bm[FP ? 0 : buf][FP ? 0 : w_jw[e] * NUM][FP ? 0 : n];
+            uint32_t w = w_reg[e];
+            int negs = 0;
+#pragma unroll
+            for (int i = 0; i < NUM; ++i) {
+                const uint32_t f = w & fmask;
+                w >>= p.dec.fw;
+                const int v0 = s.lut0[f];
+                dst[i * BN] = __int_as_float(v0);
+                if (FP) negs += int(uint32_t(v0) >> 31);
+                else dstm[i * BN] = s.lut1[f];
+            }
+            if (FP && negs) atomicAdd(&s.negc[n], negs);
+        }
+    };
+
+    auto stash = [&](int tile, int buf) {
+        const bool last = tile + 1 >= p.ntiles;
+        if (p.in_kind == DS_IN_I32) {
+            if (last) stash_a(std::true_type(), std::true_type(), tile, buf);
+            else stash_a(std::true_type(), std::false_type(), tile, buf);
+        } else {
+            stash_a(std::false_type(), std::true_type(), tile, buf);
+        }
+        switch (p.dec.num) {
+            case 4: decode_words(std::integral_constant<int, 4>(), buf); break;
+            case 5: decode_words(std::integral_constant<int, 5>(), buf); break;
+            case 6: decode_words(std::integral_constant<int, 6>(), buf); break;
+            case 8: decode_words(std::integral_constant<int, 8>(), buf); break;
+            case 10: decode_words(std::integral_constant<int, 10>(), buf); break;
+            default: decode_words(std::integral_constant<int, 16>(), buf); break;
         }
     };
 
@@ -435,114 +399,13 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     if (FP) drain();  // each thread reads back only its own slots below
 
     // ---- epilogue -----------------------------------------------------------------------------
-    // Column index of accumulator j and row index of accumulator i inside the CTA tile.
-    auto ncol = [&](int j) { return (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j); };
-    auto mrow = [&](int i) { return (i >= 4) ? (BM / 2 + 4 * tm + i - 4) : (4 * tm + i); };
-    auto accv = [&](int i, int j) -> int {
-        if (FP) return s.accs[(i * TN + j) * NT + t] - ndrains * kMagicBits;
-        return acc[FP ? 0 : i][FP ? 0 : j];
-    };
-
-    int addc[TN];
-#pragma unroll
-    for (int j = 0; j < TN; ++j) {
-        const int n = n0 + ncol(j);
-        int c = 0;
-        if (n < p.N) {
-            if (p.bias) c = __ldg(p.bias + n);
-            if (FP) c += s.negc[ncol(j)] - p.tail_neg;
-        }
-        addc[j] = c;
-    }
-
-    auto finish = [&](int v, long long oidx) -> int {
-        if (p.residual) {
-            // fp32 add of the two values as the reference's `out += identity` does it.
-            v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + oidx)));
-        }
-        if (p.relu) v = max(v, 0);
-        if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi);
-        return v;
-    };
-    int32_t* oi = static_cast<int32_t*>(p.out);
-    float* of = static_cast<float*>(p.out);
-
-    if (CONV) {
-        // 4 consecutive rows m of one column n are contiguous in NCHW when P % 4 == 0.
-        const bool vec = (p.P % 4 == 0);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int m = m0 + mrow(4 * h);
-            if (m >= p.M) continue;
-            if (vec) {
-                const int b = m / p.P, pp = m - b * p.P;
-#pragma unroll
-                for (int j = 0; j < TN; ++j) {
-                    const int n = n0 + ncol(j);
-                    if (n >= p.N) continue;
-                    const long long o = ((long long)b * p.OC + n) * p.P + pp;
-                    int v[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j) + addc[j], o + i);
-                    if (p.out_kind == DS_OUT_I32) {
-                        *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
-                    } else {
-                        *reinterpret_cast<float4*>(of + o) =
-                            make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
-                                        __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int mi = m + i;
-                    if (mi >= p.M) continue;
-                    const int b = mi / p.P, pp = mi - b * p.P;
-#pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        const int n = n0 + ncol(j);
-                        if (n >= p.N) continue;
-                        const long long o = ((long long)b * p.OC + n) * p.P + pp;
-                        const int v = finish(accv(4 * h + i, j) + addc[j], o);
-                        if (p.out_kind == DS_OUT_I32) oi[o] = v;
-                        else of[o] = __int2float_rn(v) * p.inv_scale;
-                    }
-                }
-            }
-        }
-    } else {
-        const bool vec = (p.N % 4 == 0);
-#pragma unroll
-        for (int i = 0; i < kTM; ++i) {
-            const int m = m0 + mrow(i);
-            if (m >= p.M) continue;
-#pragma unroll
-            for (int h = 0; h < TN / 4; ++h) {
-                const int n = n0 + ncol(4 * h);
-                const long long o = (long long)m * p.N + n;
-                if (vec && n + 3 < p.N) {
-                    int v[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
-                    if (p.out_kind == DS_OUT_I32) {
-                        *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
-                    } else {
-                        *reinterpret_cast<float4*>(of + o) =
-                            make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
-                                        __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (n + j >= p.N) continue;
-                        const int v = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
-                        if (p.out_kind == DS_OUT_I32) oi[o + j] = v;
-                        else of[o + j] = __int2float_rn(v) * p.inv_scale;
-                    }
-                }
-            }
-        }
-    }
+    store_tile<TN, CONV>(
+        p, m0, n0, tm, tn, BM, BN,
+        [&](int i, int j) -> int {
+            if (FP) return s.accs[(i * TN + j) * NT + t] - ndrains * kMagicBits;
+            return acc[FP ? 0 : i][FP ? 0 : j];
+        },
+        [&](int col) -> int { return FP ? (s.negc[col] - p.tail_neg) : 0; });
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -601,6 +464,12 @@ template <int AM>
 int launch_am(const GemmParams& p, bool fp, cudaStream_t st)
 {
     if (fp) {
+        // Convolutions run on the warp-specialised kernel; the linear layer (x rows are
+        // contiguous in k) stages faster with all 16 warps doing their share.
+        if (AM != AM_LINEAR) {
+            const int rc = launch_ws(p, AM, st);
+            if (rc != DS_ERR_UNSUPPORTED) return rc;
+        }
         if (p.N > 64) return launch_cfg<512, 32, 16, 8, 28, MODE_FP, AM>(p, st);
         return launch_cfg<512, 32, 16, 4, 28, MODE_FP, AM>(p, st);
     }
@@ -718,7 +587,7 @@ extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t*
     const int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
     const long long M = (long long)B * OH * OW, Kll = (long long)C * KH * KW;
     if (M > 2147483647LL || Kll > 2147483647LL || (long long)C * H * W > 2147483647LL) return DS_ERR_RANGE;
-    if ((long long)B * C * H * W * 4 >= (1ll << 32)) return DS_ERR_RANGE;  // 32-bit byte offsets into x
+    if ((long long)C * H * W * 4 >= (1ll << 31)) return DS_ERR_RANGE;  // int byte offsets inside one image
     if (Kll * KH * KW >= (1ll << 32)) return DS_ERR_RANGE;                 // exactness of the magic division
     GemmParams p = {};
     p.x = x; p.packed = packed; p.bias = bias; p.out = out;

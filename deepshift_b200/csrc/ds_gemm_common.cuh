@@ -1,0 +1,189 @@
+// Declarations shared by the two GEMM/convolution kernels (ds_gemm.cu, ds_gemm_ws.cu).
+#pragma once
+#include <cstddef>
+#include <type_traits>
+
+#include "ds_common.cuh"
+
+namespace ds {
+
+constexpr int kTM = 8;  // rows of x per thread
+constexpr int kPadMarker = 0x7FC0DEAD;  // NaN pattern standing for "integer 0, do not quantise"
+constexpr int MODE_INT = 0, MODE_FP = 1;
+constexpr int AM_LINEAR = -1, AM_TABLE = 0;  // AM >= 1: row mode with KW = AM
+
+struct GemmParams {
+    const void* x;        // int32 or fp32
+    const int32_t* packed;
+    const int32_t* bias;  // may be null
+    void* out;            // int32 or fp32
+    const int32_t* residual;
+    int M, K, N;
+    Decode dec;
+    int kt_words;     // packed words per row per k-tile
+    int bk;           // k values per tile = kt_words * num
+    int ntiles;       // ceil(row_len / kt_words)
+    int flush_tiles;  // FP path: tiles between drains of the float accumulators
+    int tail_neg;     // FP path: slots k >= K inside the last tile; each decodes as a negative weight
+    // convolution geometry
+    int C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW, P;  // P = OH*OW
+    unsigned magic_khw, magic_kw, magic_kh;  // ceil(2^32 / d), 0 for d == 1: __umulhi(k, magic) == k / d
+    int rows_per_tile;  // row mode: (ic,kh) rows per k-tile = bk / KW
+    // fused prologue / epilogue
+    int in_kind, out_kind, relu, requant;
+    Quant q;
+    int rq_lo, rq_hi;
+    float inv_scale;  // 2^-F
+};
+
+struct alignas(16) KEntry {
+    int off;  // byte offset of the tap (table mode) or of the row start (row mode)
+    int kh;   // 31 marks an entry past the end of K (bit 31 of a row mask is never set)
+    int kw;
+    int pad;
+};
+
+__device__ __forceinline__ void red_shared_add(int* addr, int v)
+{
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(addr)), "r"(v)
+                 : "memory");
+}
+
+__device__ __forceinline__ int magic_div(int k, unsigned magic) { return magic ? int(__umulhi(unsigned(k), magic)) : k; }
+
+
+// Epilogue shared by both kernels: v = acc + bias (+ negative-weight count), optional residual
+// add, ReLU, requantise clamp, then int32 or fp32 store.  Thread (tm, tn) owns rows
+// 4*tm..4*tm+3 and BM/2 + the same, and columns 4*tn..4*tn+3 (and BN/2 + the same when TN == 8)
+// of the CTA tile at (m0, n0).  `accv(i, j)` returns the finished integer sum, `colc(j)` the
+// per-column constant added to it.
+template <int TN, bool CONV, class AccFn, class ColFn>
+__device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, int tm, int tn, int BM, int BN,
+                                           AccFn accv, ColFn colc)
+{
+    auto ncol = [&](int j) { return (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j); };
+    auto mrow = [&](int i) { return (i >= 4) ? (BM / 2 + 4 * tm + i - 4) : (4 * tm + i); };
+    int addc[TN];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+        const int n = n0 + ncol(j);
+        int c = 0;
+        if (n < p.N) {
+            if (p.bias) c = __ldg(p.bias + n);
+            c += colc(ncol(j));
+        }
+        addc[j] = c;
+    }
+    auto finish = [&](int v, long long oidx) -> int {
+        if (p.residual) {
+            // fp32 add of the two values as the reference's `out += identity` does it.
+            v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + oidx)));
+        }
+        if (p.relu) v = max(v, 0);
+        if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi);
+        return v;
+    };
+    int32_t* oi = static_cast<int32_t*>(p.out);
+    float* of = static_cast<float*>(p.out);
+
+    if (CONV) {
+        // 4 consecutive rows m of one column n are contiguous in NCHW when P % 4 == 0.
+        const bool vec = (p.P % 4 == 0);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int m = m0 + mrow(4 * h);
+            if (m >= p.M) continue;
+            if (vec) {
+                const int b = m / p.P, pp = m - b * p.P;
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    const int n = n0 + ncol(j);
+                    if (n >= p.N) continue;
+                    const long long o = ((long long)b * p.OC + n) * p.P + pp;
+                    int v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j) + addc[j], o + i);
+                    if (p.out_kind == DS_OUT_I32) {
+                        *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
+                    } else {
+                        *reinterpret_cast<float4*>(of + o) =
+                            make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
+                                        __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int mi = m + i;
+                    if (mi >= p.M) continue;
+                    const int b = mi / p.P, pp = mi - b * p.P;
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) {
+                        const int n = n0 + ncol(j);
+                        if (n >= p.N) continue;
+                        const long long o = ((long long)b * p.OC + n) * p.P + pp;
+                        const int v = finish(accv(4 * h + i, j) + addc[j], o);
+                        if (p.out_kind == DS_OUT_I32) oi[o] = v;
+                        else of[o] = __int2float_rn(v) * p.inv_scale;
+                    }
+                }
+            }
+        }
+    } else {
+        const bool vec = (p.N % 4 == 0);
+#pragma unroll
+        for (int i = 0; i < kTM; ++i) {
+            const int m = m0 + mrow(i);
+            if (m >= p.M) continue;
+#pragma unroll
+            for (int h = 0; h < TN / 4; ++h) {
+                const int n = n0 + ncol(4 * h);
+                const long long o = (long long)m * p.N + n;
+                if (vec && n + 3 < p.N) {
+                    int v[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
+                    if (p.out_kind == DS_OUT_I32) {
+                        *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
+                    } else {
+                        *reinterpret_cast<float4*>(of + o) =
+                            make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
+                                        __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (n + j >= p.N) continue;
+                        const int v = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
+                        if (p.out_kind == DS_OUT_I32) oi[o + j] = v;
+                        else of[o + j] = __int2float_rn(v) * p.inv_scale;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Fixed-point value v (int32 bits, or fp32 bits for the fp32 input kinds) as the operand the
+// kernels keep in shared memory: x + 0.5 as a float on the FP path, x as int bits otherwise.
+template <bool FP, bool IN32>
+__device__ __forceinline__ float operand_of(const GemmParams& p, int v)
+{
+    if (IN32) {
+        // x + 0.5 without an int->float conversion: adding 2x+1 to the bits of 1.5*2^22
+        // (ulp 0.5) gives 1.5*2^22 + x + 0.5 exactly for |x| < 2^20.
+        return FP ? (__int_as_float(2 * v + (kHalfMagicBits + 1)) - kHalfMagic) : __int_as_float(v);
+    }
+    float f;  // the quantised value, an integer held in a float
+    if (v == kPadMarker) f = 0.f;
+    else if (p.in_kind == DS_IN_F32_CONV) f = quant_conv_f(__int_as_float(v), p.q);
+    else f = truncf(__int_as_float(v) * p.q.scale);
+    return FP ? (f + 0.5f) : __int_as_float(__float2int_rz(f));
+}
+
+// Warp-specialised FP32-pipe kernel (ds_gemm_ws.cu).  am: AM_LINEAR, AM_TABLE or the window
+// width of the row mode.  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller then
+// falls back to the table mode or the integer path.
+int launch_ws(const GemmParams& p, int am, cudaStream_t st);
+
+}  // namespace ds

@@ -1,0 +1,481 @@
+// Warp-specialised FP32-pipe shift "GEMM" / convolution for sm_100a.
+//
+// Arithmetic: see ds_gemm.cu (one FFMA with round-toward-minus-infinity per term, magic-offset
+// accumulators drained into shared int32 slots).  This file changes how the work is divided:
+//
+//   * 16 consumer warps (512 threads) own a 256 x BN output tile, 8 x TN outputs per thread.
+//     Their loop is nothing but shared-memory fragment loads and FFMAs; they never touch
+//     global memory before the epilogue and never wait on another consumer warp.
+//   * 8 producer warps (256 threads) gather x (implicit im2col, zero padding by predication,
+//     int32 -> x + 0.5 conversion or the fused fp32 quantiser), fetch the packed weight words
+//     and decode them through the lookup table, one k-tile ahead of the consumers.
+//   * The two groups meet only at mbarriers: full[s] (256 producer arrivals) and empty[s] (512
+//     consumer arrivals) for each of the two stages.  Global-load latency, the decode chains
+//     and the stores of a stage all overlap the FFMA stream of the previous stage, so the
+//     FMA pipe no longer idles while "everybody stages".
+//
+// Every wait is bounded: a wait that runs out records an error and lets the thread continue,
+// so the kernel always terminates; the host can read the flag with ds_last_kernel_error().
+#include "ds_gemm_common.cuh"
+
+namespace ds {
+namespace {
+
+constexpr int WS_CONS = 512;   // consumer threads
+constexpr int WS_PROD = 256;   // producer threads
+constexpr int WS_NT = WS_CONS + WS_PROD;
+constexpr int WS_BM = 256;     // rows of x per CTA
+constexpr int WS_BKT = 28;     // largest k-tile
+constexpr int WS_STAGES = 2;
+// Register split after the roles part.  The CTA starts with 768 * 80 registers; what the
+// producers give back (256 * (80 - 48) = 8192) is all the consumers can take (512 * (96 - 80) =
+// 8192): a larger request would wait for registers that never come.
+constexpr int WS_LAUNCH_REGS = 80, WS_PROD_REGS = 48, WS_CONS_REGS = 96;
+static_assert(WS_CONS * (WS_CONS_REGS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - WS_PROD_REGS), "register pool");
+constexpr int WS_WAIT_LIMIT = 1 << 20;  // polls of one mbarrier wait before giving up
+
+__device__ int g_ws_error = 0;  // set when a bounded wait ran out (never in a correct run)
+
+template <int TN>
+struct WsSmem {
+    static constexpr int BN = 16 * TN;
+    static constexpr int AP = WS_BM + 4;
+    alignas(16) float a[WS_STAGES][WS_BKT][AP];  // x + 0.5
+    alignas(16) float b[WS_STAGES][WS_BKT][BN];  // +-2^-r
+    alignas(16) KEntry ktab[WS_STAGES][WS_BKT];
+    alignas(8) unsigned long long full[WS_STAGES];
+    alignas(8) unsigned long long empty[WS_STAGES];
+    int lut0[256];  // float bits of the decoded weight per field value
+    int negc[BN];   // negative weights per output column
+    int err;
+    int accs[kTM * TN * WS_CONS];  // drained accumulators, [slot][consumer thread]
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
+{
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait for the phase with the given parity to complete.  Returns false on give-up.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity)
+{
+    const unsigned addr = smem_u32(bar);
+    for (int i = 0; i < WS_WAIT_LIMIT; ++i) {
+        unsigned ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        __nanosleep(32);  // leave the issue slots to the warps that make progress
+    }
+    return false;
+}
+
+__device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(WS_PROD) : "memory"); }
+
+// ---------------------------------------------------------------------------------------------
+template <int TN, int AM>
+__global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
+{
+    using S = WsSmem<TN>;
+    constexpr bool CONV = AM != AM_LINEAR;
+    constexpr bool ROW = AM >= 1;
+    constexpr int KW = ROW ? AM : 1;
+    constexpr int BM = WS_BM, BN = S::BN;
+    constexpr int TMG = 32, TNG = 16;
+    static_assert(offsetof(S, b) % 16 == 0 && offsetof(S, ktab) % 16 == 0 && offsetof(S, full) % 8 == 0, "alignment");
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    S& s = *reinterpret_cast<S*>(smem_raw);
+
+    const int t = threadIdx.x;
+    const int m0 = blockIdx.x * BM;
+    const int n0 = blockIdx.y * BN;
+
+    // ---- set-up by all 640 threads ----------------------------------------------------------------
+    for (int f = t; f < (1 << p.dec.fw); f += WS_NT) {
+        int neg;
+        s.lut0[f] = __float_as_int(decode_f32(uint32_t(f), p.dec, true, neg));
+    }
+    for (int i = t; i < BN; i += WS_NT) s.negc[i] = 0;
+    if (t < WS_CONS) {
+#pragma unroll
+        for (int q = 0; q < kTM * TN; ++q) s.accs[q * WS_CONS + t] = 0;
+    }
+    if (t == 0) {
+        for (int i = 0; i < WS_STAGES; ++i) {
+            mbar_init(&s.full[i], WS_PROD);
+            mbar_init(&s.empty[i], WS_CONS);
+        }
+        s.err = 0;
+    }
+    __syncthreads();
+
+    if (t >= WS_CONS) {
+        // =========================== producers ==================================================
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_PROD_REGS));
+        const int pt = t - WS_CONS;
+        constexpr int PIX = BM / WS_PROD;  // 2 rows of the x tile per producer thread (conv)
+        const char* x_pix[PIX];
+        uint32_t rowmask[PIX], colmask[PIX];
+        if (CONV) {
+#pragma unroll
+            for (int q = 0; q < PIX; ++q) {
+                const int m = m0 + pt + q * WS_PROD;
+                x_pix[q] = reinterpret_cast<const char*>(p.x);
+                rowmask[q] = colmask[q] = 0;
+                if (m < p.M) {
+                    const int b = m / p.P, pp = m - b * p.P;
+                    const int oh = pp / p.OW, ow = pp - oh * p.OW;
+                    const int ih0 = oh * p.sh - p.ph, iw0 = ow * p.sw - p.pw;
+                    for (int kh = 0; kh < p.KH; ++kh)
+                        if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[q] |= 1u << kh;
+                    for (int kw = 0; kw < p.KW; ++kw)
+                        if (unsigned(iw0 + kw) < unsigned(p.W)) colmask[q] |= 1u << kw;
+                    // address of (b, 0, ih0, iw0): may lie outside the tensor, only valid taps are read
+                    x_pix[q] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4;
+                }
+            }
+        }
+        // weight words: column n = wi % BN, word jw = wi / BN of the k-tile, wi = pt + WS_PROD * e
+        constexpr int EW = (BN * (WS_BKT / 4) + WS_PROD - 1) / WS_PROD;
+        const int wn = pt & (BN - 1);
+        const int32_t* wrow = (n0 + wn < p.N) ? p.packed + (long long)(n0 + wn) * p.dec.row_len : nullptr;
+        const uint32_t fmask = (1u << p.dec.fw) - 1u;
+
+        // Gathers and stores the x tile of one k-tile.  IN32: int32 input kind; LAST: the tile may
+        // reach past K, where x is stored as 0 (see the weight tail below).
+        auto stage_x = [&](auto in32_tag, auto last_tag, int st, int k0) {
+            constexpr bool IN32 = decltype(in32_tag)::value;
+            constexpr bool LAST = decltype(last_tag)::value;
+            const int padv = IN32 ? 0 : kPadMarker;
+            if (ROW) {
+                // UR rows of the k-tile at a time: 2 * UR * KW loads in flight per thread
+                constexpr int UR = (KW == 1) ? 4 : (KW == 3 ? 4 : 2);
+                for (int r0 = 0; r0 < p.rows_per_tile; r0 += UR) {
+                    int v[PIX][UR][KW];
+#pragma unroll
+                    for (int u = 0; u < UR; ++u) {
+                        const int2 e = *reinterpret_cast<const int2*>(&s.ktab[st][r0 + u]);
+#pragma unroll
+                        for (int q = 0; q < PIX; ++q) {
+                            const bool rv = (rowmask[q] >> e.y) & 1u;
+                            const int* rowp = reinterpret_cast<const int*>(x_pix[q] + e.x);
+#pragma unroll
+                            for (int kw = 0; kw < KW; ++kw) {
+                                int val = padv;
+                                if (rv && (colmask[q] & (1u << kw))) val = __ldg(rowp + kw);
+                                v[q][u][kw] = val;
+                            }
+                        }
+                    }
+                    float* dst = &s.a[st][r0 * KW][pt];
+#pragma unroll
+                    for (int u = 0; u < UR; ++u)
+#pragma unroll
+                        for (int q = 0; q < PIX; ++q)
+#pragma unroll
+                            for (int kw = 0; kw < KW; ++kw) {
+                                float o = operand_of<true, IN32>(p, v[q][u][kw]);
+                                if (LAST && k0 + (r0 + u) * KW + kw >= p.K) o = 0.f;
+                                dst[(u * KW + kw) * S::AP + q * WS_PROD] = o;
+                            }
+                }
+            } else if (CONV) {
+                constexpr int UK = 4;  // columns of the k-tile at a time
+                for (int kb = 0; kb < p.bk; kb += UK) {
+                    int v[PIX][UK];
+#pragma unroll
+                    for (int u = 0; u < UK; ++u) {
+                        const int4 e = *reinterpret_cast<const int4*>(&s.ktab[st][kb + u]);
+#pragma unroll
+                        for (int q = 0; q < PIX; ++q) {
+                            int val = padv;
+                            if (((rowmask[q] >> e.y) & (colmask[q] >> e.z) & 1u) != 0u)
+                                val = __ldg(reinterpret_cast<const int*>(x_pix[q] + e.x));
+                            v[q][u] = val;
+                        }
+                    }
+                    float* dst = &s.a[st][kb][pt];
+#pragma unroll
+                    for (int u = 0; u < UK; ++u)
+#pragma unroll
+                        for (int q = 0; q < PIX; ++q) {
+                            float o = operand_of<true, IN32>(p, v[q][u]);
+                            if (LAST && k0 + kb + u >= p.K) o = 0.f;
+                            dst[u * S::AP + q * WS_PROD] = o;
+                        }
+                }
+            } else {
+                // x is [M,K]: lanes run along k (32 wide), RP rows per pass, UP passes at a time
+                constexpr int RP = WS_PROD / 32;
+                const int kl = pt & 31;
+                const bool kval = kl < p.bk && k0 + kl < p.K;
+                constexpr int UP = 8;
+                for (int mb = 0; mb < BM; mb += RP * UP) {
+                    int v[UP];
+#pragma unroll
+                    for (int u = 0; u < UP; ++u) {
+                        const int ml = mb + RP * u + (pt >> 5);
+                        int val = padv;
+                        if (kval && m0 + ml < p.M)
+                            val = __ldg(static_cast<const int32_t*>(p.x) + ((long long)(m0 + ml) * p.K + k0 + kl));
+                        v[u] = val;
+                    }
+                    if (kl < WS_BKT) {
+#pragma unroll
+                        for (int u = 0; u < UP; ++u) {
+                            const int ml = mb + RP * u + (pt >> 5);
+                            float o = operand_of<true, IN32>(p, v[u]);
+                            if (LAST && k0 + kl >= p.K) o = 0.f;
+                            s.a[st][kl][ml] = o;
+                        }
+                    }
+                }
+            }
+        };
+
+        for (int tile = 0; tile < p.ntiles; ++tile) {
+            const int st = tile & 1;
+            if (tile >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned((tile >> 1) - 1) & 1u)) s.err = 1;
+            const int k0 = tile * p.bk;
+            const bool last = tile + 1 >= p.ntiles;
+
+            // weight words of this tile (issued first: their latency hides behind the x gather)
+            uint32_t w_reg[EW];
+            const int w0 = tile * p.kt_words;
+#pragma unroll
+            for (int e = 0; e < EW; ++e) {
+                const int jw = (pt + e * WS_PROD) / BN;
+                uint32_t w = 0;
+                if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len) w = uint32_t(__ldg(wrow + w0 + jw));
+                w_reg[e] = w;
+            }
+
+            // per-tile table of k -> (offset, kh[, kw])
+            if (CONV && pt < WS_BKT) {
+                KEntry e;
+                e.pad = 0;
+                e.off = 0;
+                e.kh = 31;
+                e.kw = 0;
+                if (ROW) {
+                    const int row = tile * p.rows_per_tile + pt;  // global (ic,kh) row index
+                    if (pt < p.rows_per_tile && row < p.C * p.KH) {
+                        const int ic = magic_div(row, p.magic_kh);
+                        e.kh = row - ic * p.KH;
+                        e.off = (ic * p.H * p.W + e.kh * p.W) * 4;
+                    }
+                } else {
+                    const int k = k0 + pt;
+                    if (pt < p.bk && k < p.K) {
+                        const int ic = magic_div(k, p.magic_khw);
+                        const int tap = k - ic * (p.KH * p.KW);
+                        e.kh = magic_div(tap, p.magic_kw);
+                        e.kw = tap - e.kh * p.KW;
+                        e.off = (ic * p.H * p.W + e.kh * p.W + e.kw) * 4;
+                    }
+                }
+                s.ktab[st][pt] = e;
+            }
+            if (CONV) producer_bar();
+
+            if (p.in_kind == DS_IN_I32) {
+                if (last) stage_x(std::true_type(), std::true_type(), st, k0);
+                else stage_x(std::true_type(), std::false_type(), st, k0);
+            } else {
+                stage_x(std::false_type(), std::true_type(), st, k0);
+            }
+
+            // ---- weight tile: decode through the table ------------------------------------------------
+            // Slots k >= K of the last words decode like any field (a zero field is -2^0); the x
+            // values stored above are 0 there, so they add nothing, and the epilogue takes their
+            // share (tail_neg) out of the negative-weight count.
+            int negs = 0;
+            auto decode = [&](auto num_tag) {
+                constexpr int NUM = decltype(num_tag)::value;
+#pragma unroll
+                for (int e = 0; e < EW; ++e) {
+                    const int jw = (pt + e * WS_PROD) / BN;
+                    if (jw < p.kt_words) {
+                        uint32_t w = w_reg[e];
+                        float* dst = &s.b[st][jw * NUM][wn];
+#pragma unroll
+                        for (int i = 0; i < NUM; ++i) {
+                            const int v0 = s.lut0[w & fmask];
+                            w >>= p.dec.fw;
+                            dst[i * BN] = __int_as_float(v0);
+                            negs += int(uint32_t(v0) >> 31);
+                        }
+                    }
+                }
+            };
+            switch (p.dec.num) {
+                case 4: decode(std::integral_constant<int, 4>()); break;
+                case 5: decode(std::integral_constant<int, 5>()); break;
+                case 6: decode(std::integral_constant<int, 6>()); break;
+                case 8: decode(std::integral_constant<int, 8>()); break;
+                case 10: decode(std::integral_constant<int, 10>()); break;
+                default: decode(std::integral_constant<int, 16>()); break;
+            }
+            if (negs) atomicAdd(&s.negc[wn], negs);
+            mbar_arrive(&s.full[st]);
+        }
+        if (s.err) g_ws_error = 1;
+        return;
+    }
+
+    // =============================== consumers ====================================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_CONS_REGS));
+    // A warp covers 8 x 4 thread tiles, 8 along the direction in which the output is contiguous.
+    const int lane = t & 31, warp = t >> 5;
+    int tm, tn;
+    if (CONV) {
+        constexpr int WMG = TMG / 8;
+        tm = (warp % WMG) * 8 + (lane & 7);
+        tn = (warp / WMG) * 4 + (lane >> 3);
+    } else {
+        constexpr int WNG = TNG / 8;
+        tn = (warp % WNG) * 8 + (lane & 7);
+        tm = (warp / WNG) * 4 + (lane >> 3);
+    }
+    float accf[kTM][TN];
+#pragma unroll
+    for (int i = 0; i < kTM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) accf[i][j] = kMagic;
+
+    int ndrains = 0, since = 0;
+    bool bad = false;
+    for (int tile = 0; tile < p.ntiles; ++tile) {
+        const int st = tile & 1;
+        if (!mbar_wait(&s.full[st], unsigned(tile >> 1) & 1u)) bad = true;
+#pragma unroll 4
+        for (int k = 0; k < p.bk; ++k) {
+            float a[kTM], b[TN];
+            *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
+            *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&s.a[st][k][BM / 2 + 4 * tm]);
+            *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s.b[st][k][4 * tn]);
+            if (TN == 8)
+                *reinterpret_cast<float4*>(&b[TN - 4]) = *reinterpret_cast<const float4*>(&s.b[st][k][BN / 2 + 4 * tn]);
+#pragma unroll
+            for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
+        }
+        mbar_arrive(&s.empty[st]);
+        if (++since == p.flush_tiles || tile + 1 == p.ntiles) {
+            // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
+            // slots and restart them; the epilogue removes ndrains * kMagicBits.
+#pragma unroll
+            for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    red_shared_add(&s.accs[(i * TN + j) * WS_CONS + t], __float_as_int(accf[i][j]));
+                    accf[i][j] = kMagic;
+                }
+            ++ndrains;
+            since = 0;
+        }
+    }
+    if (bad) g_ws_error = 1;
+
+    store_tile<TN, CONV>(
+        p, m0, n0, tm, tn, BM, BN,
+        [&](int i, int j) -> int { return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits; },
+        [&](int col) -> int { return s.negc[col] - p.tail_neg; });
+}
+
+// Chooses the k-tile: a multiple of num (whole packed words) and of the staging granularity
+// (row mode: UR whole rows; table mode: 4 columns), at most WS_BKT.
+template <int AM>
+bool ws_choose_tile(GemmParams& p)
+{
+    constexpr int KW = AM >= 1 ? AM : 1;
+    constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : (AM == AM_TABLE ? 4 : 1);
+    int best = 0;
+    for (int bk = WS_BKT; bk >= 2 && !best; --bk)
+        if (bk % p.dec.num == 0 && bk % GRAN == 0) best = bk;
+    if (!best) return false;
+    p.bk = best;
+    p.kt_words = best / p.dec.num;
+    p.rows_per_tile = best / KW;
+    p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
+    // Every slot from K to the end of the last tile decodes from a zero field, i.e. as -2^0.
+    p.tail_neg = p.ntiles * p.bk - p.K;
+    p.flush_tiles /= p.bk;  // the caller left the number of terms that cannot overflow
+    if (p.flush_tiles > 4096) p.flush_tiles = 4096;
+    return p.flush_tiles >= 1;
+}
+
+template <int TN, int AM>
+int ws_launch_cfg(GemmParams p, cudaStream_t st)
+{
+    using S = WsSmem<TN>;
+    if (!ws_choose_tile<AM>(p)) return DS_ERR_UNSUPPORTED;
+    auto kern = ws_kernel<TN, AM>;
+    const size_t smem = sizeof(S);
+    static int attr_state = 0;  // per instantiation: 0 unknown, 1 usable, -1 not usable
+    if (attr_state == 0) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+            cudaGetLastError();
+            return DS_ERR_CUDA;
+        }
+        // The register hand-over in the kernel is sized for this launch allocation; with any
+        // other one the consumers could wait for registers for ever, so the kernel is not used.
+        attr_state = (fa.numRegs == WS_LAUNCH_REGS) ? 1 : -1;
+    }
+    if (attr_state < 0) return DS_ERR_UNSUPPORTED;
+    const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
+    if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
+    kern<<<dim3((unsigned)gx, (unsigned)gy), WS_NT, smem, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
+template <int AM>
+int ws_launch_am(const GemmParams& p, cudaStream_t st)
+{
+    if (p.N > 64) return ws_launch_cfg<8, AM>(p, st);  // 256 x 128
+    return ws_launch_cfg<4, AM>(p, st);                // 256 x 64
+}
+
+}  // namespace
+
+int launch_ws(const GemmParams& p, int am, cudaStream_t st)
+{
+    switch (am) {
+        case AM_LINEAR: return ws_launch_am<AM_LINEAR>(p, st);
+        case AM_TABLE: return ws_launch_am<AM_TABLE>(p, st);
+        case 1: return ws_launch_am<1>(p, st);
+        case 3: return ws_launch_am<3>(p, st);
+        case 5: return ws_launch_am<5>(p, st);
+        case 7: return ws_launch_am<7>(p, st);
+        default: return DS_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace ds
+
+// Reads and clears the flag that a kernel sets when one of its bounded waits ran out.
+// Synchronises the device.  0 = no error.
+extern "C" int ds_last_kernel_error(int* flag)
+{
+    if (!flag) return DS_ERR_BAD_ARG;
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, ds::g_ws_error, sizeof(int)) != cudaSuccess) return DS_ERR_CUDA;
+    const int zero = 0;
+    if (v && cudaMemcpyToSymbol(ds::g_ws_error, &zero, sizeof(int)) != cudaSuccess) return DS_ERR_CUDA;
+    *flag = v;
+    return DS_OK;
+}

@@ -132,6 +132,13 @@ int ds_quantize_f32(const float *x, int32_t *out, long long n, int kind, int act
  */
 int ds_pipe_peak(int mode, int iters, double *ops_per_s, void *stream);
 
+/*
+ * Reads and clears the device-side flag that a kernel of this library sets when one of its
+ * bounded waits ran out (its output is then undefined; it never happens in a correct run).
+ * Synchronises the current device.  *flag = 0 means no error.
+ */
+int ds_last_kernel_error(int *flag);
+
 const char *ds_strerror(int status);
 int ds_version(void);
 
