@@ -20,11 +20,11 @@ class Fuse(ctypes.Structure):
         ("act_integer_bits", ctypes.c_int), ("act_fraction_bits", ctypes.c_int),
         ("relu", ctypes.c_int), ("requant", ctypes.c_int),
         ("residual", ctypes.c_void_p), ("act_bits", ctypes.c_int),
-        ("reserved", ctypes.c_int * 4),
+        ("round_f32", ctypes.c_int), ("reserved", ctypes.c_int * 3),
     ]
 
 
-IN_I32, IN_F32_CONV, IN_F32_LINEAR = 0, 1, 2
+IN_I32, IN_F32_CONV, IN_F32_LINEAR, IN_I32_CLAMP = 0, 1, 2, 3
 OUT_I32, OUT_F32 = 0, 1
 
 _VP, _I, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
@@ -35,6 +35,8 @@ _SIGNATURES = {
     "ds_conv2d_ex": [_VP, _VP, _VP, _VP] + [_I] * 13 + [ctypes.POINTER(Fuse), _VP],
     "ds_compress": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "ds_quantize_f32": [_VP, _VP, _LL, _I, _I, _I, _VP],
+    "ds_maxpool2d_i32": [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
+    "ds_avgpool_fix_i32": [_VP, _VP, _I, _I, _I, _I, _I, _VP],
     "ds_pipe_peak": [_I, _I, ctypes.POINTER(ctypes.c_double), _VP],
     "ds_last_kernel_error": [ctypes.POINTER(ctypes.c_int)],
 }

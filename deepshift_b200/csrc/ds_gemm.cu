@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     // the image or the matrix carry a marker so that stash() stores the integer 0 there
     // without quantising it.
     auto fetch = [&](int tile, int buf) {
-        const int padv = (p.in_kind == DS_IN_I32) ? 0 : kPadMarker;
+        const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
         if (ROW) {
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
@@ -253,7 +253,8 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 
     // Convert and store the x registers into shared buffer `buf`.  LAST: the tile may reach past
     // K, where x is stored as 0 (see decode_word).
-    auto stash_a = [&](auto in32_tag, auto last_tag, int tile, int buf) {
+    auto stash_a = [&](auto ink_tag, auto last_tag, int tile, int buf) {
+        constexpr int INK = decltype(ink_tag)::value;
         constexpr bool LAST = decltype(last_tag)::value;
         const int k0 = tile * p.bk;
         if (ROW) {
@@ -263,7 +264,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 #pragma unroll
                 for (int kw = 0; kw < KW; ++kw) {
                     const int kl = r * KW + kw;
-                    float o = operand_of<FP, decltype(in32_tag)::value>(p, a_reg[u * KW + kw]);
+                    float o = operand_of<FP, INK>(p, a_reg[u * KW + kw]);
                     if (LAST && k0 + kl >= p.K) o = 0.f;
                     s.a[buf][kl][a_m] = o;
                 }
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
                 const int kl = CONV ? (a_k + e * A_KSTEP) : a_k;
                 const int ml = CONV ? a_m : (a_m + e * A_MSTEP);
                 if (kl < BKT && ml < BM) {
-                    float o = operand_of<FP, decltype(in32_tag)::value>(p, a_reg[e]);
+                    float o = operand_of<FP, INK>(p, a_reg[e]);
                     if (LAST && k0 + kl >= p.K) o = 0.f;
                     s.a[buf][kl][ml] = o;
                 }
@@ -311,12 +312,10 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 
     auto stash = [&](int tile, int buf) {
         const bool last = tile + 1 >= p.ntiles;
-        if (p.in_kind == DS_IN_I32) {
-            if (last) stash_a(std::true_type(), std::true_type(), tile, buf);
-            else stash_a(std::true_type(), std::false_type(), tile, buf);
-        } else {
-            stash_a(std::false_type(), std::true_type(), tile, buf);
-        }
+        with_input_kind(p, [&](auto ink_tag) {
+            if (last) stash_a(ink_tag, std::true_type(), tile, buf);
+            else stash_a(ink_tag, std::false_type(), tile, buf);
+        });
         switch (p.dec.num) {
             case 4: decode_words(std::integral_constant<int, 4>(), buf); break;
             case 5: decode_words(std::integral_constant<int, 5>(), buf); break;
@@ -503,22 +502,24 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.dec.row_len = (p.K + p.dec.num - 1) / p.dec.num;
     ds_fuse_t f = {};
     if (fuse) f = *fuse;
-    if (f.in_kind < 0 || f.in_kind > 2 || f.out_kind < 0 || f.out_kind > 1) return DS_ERR_BAD_ARG;
+    if (f.in_kind < 0 || f.in_kind > 3 || f.out_kind < 0 || f.out_kind > 1) return DS_ERR_BAD_ARG;
     const int I = f.act_integer_bits, F = f.act_fraction_bits;
+    const bool in_clamp = f.in_kind == DS_IN_I32_CLAMP;
     const bool needs_if = f.in_kind != DS_IN_I32 || f.out_kind != DS_OUT_I32 || f.requant;
     if (needs_if && (F < 0 || F > 30)) return DS_ERR_BAD_ARG;
-    if ((f.in_kind == DS_IN_F32_CONV || f.requant) && (I < 1 || I + F > 31)) return DS_ERR_BAD_ARG;
+    if ((f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp) && (I < 1 || I + F > 31)) return DS_ERR_BAD_ARG;
     p.in_kind = f.in_kind;
     p.out_kind = f.out_kind;
     p.relu = f.relu;
     p.requant = f.requant;
+    p.round_f32 = f.round_f32;
     p.residual = f.residual;
     p.q.scale = float(1ll << (needs_if ? F : 0));
     p.inv_scale = 1.0f / p.q.scale;
     p.q.sign_mode = (f.in_kind == DS_IN_F32_CONV && I == 1);
     p.q.lo = p.q.hi = 0.f;
     p.rq_lo = p.rq_hi = 0;
-    if (f.in_kind == DS_IN_F32_CONV || f.requant) {
+    if (f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp) {
         const long long lo = -(1ll << (I - 1 + F)), hi = ((1ll << (I - 1)) - 1) * (1ll << F);
         p.q.lo = float(lo);
         p.q.hi = float(hi);
@@ -529,6 +530,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     // least one k-tile of terms (each of magnitude <= 2^(act_bits-1) + 1) between drains.
     int ab = f.act_bits;
     if (f.in_kind == DS_IN_F32_CONV) ab = p.q.sign_mode ? F + 2 : I + F;
+    if (in_clamp) ab = I + F;
     if (f.in_kind == DS_IN_F32_LINEAR) ab = 0;
     use_fp = (base == 0 && ab >= 1 && ab <= 18);
     p.flush_tiles = 0;

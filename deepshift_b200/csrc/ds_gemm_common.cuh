@@ -30,7 +30,7 @@ struct GemmParams {
     unsigned magic_khw, magic_kw, magic_kh;  // ceil(2^32 / d), 0 for d == 1: __umulhi(k, magic) == k / d
     int rows_per_tile;  // row mode: (ic,kh) rows per k-tile = bk / KW
     // fused prologue / epilogue
-    int in_kind, out_kind, relu, requant;
+    int in_kind, out_kind, relu, requant, round_f32;
     Quant q;
     int rq_lo, rq_hi;
     float inv_scale;  // 2^-F
@@ -81,6 +81,7 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
         }
         if (p.relu) v = max(v, 0);
         if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi);
+        if (p.round_f32) v = __float2int_rn(__int2float_rn(v));
         return v;
     };
     int32_t* oi = static_cast<int32_t*>(p.out);
@@ -166,10 +167,14 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
 
 // Fixed-point value v (int32 bits, or fp32 bits for the fp32 input kinds) as the operand the
 // kernels keep in shared memory: x + 0.5 as a float on the FP path, x as int bits otherwise.
-template <bool FP, bool IN32>
+// INK selects the input kind at compile time: INK_I32, INK_I32_CLAMP or INK_F32 (either fp32 kind).
+constexpr int INK_I32 = 0, INK_F32 = 1, INK_I32_CLAMP = 2;
+
+template <bool FP, int INK>
 __device__ __forceinline__ float operand_of(const GemmParams& p, int v)
 {
-    if (IN32) {
+    if (INK != INK_F32) {
+        if (INK == INK_I32_CLAMP) v = min(max(v, p.rq_lo), p.rq_hi);
         // x + 0.5 without an int->float conversion: adding 2x+1 to the bits of 1.5*2^22
         // (ulp 0.5) gives 1.5*2^22 + x + 0.5 exactly for |x| < 2^20.
         return FP ? (__int_as_float(2 * v + (kHalfMagicBits + 1)) - kHalfMagic) : __int_as_float(v);
@@ -179,6 +184,15 @@ __device__ __forceinline__ float operand_of(const GemmParams& p, int v)
     else if (p.in_kind == DS_IN_F32_CONV) f = quant_conv_f(__int_as_float(v), p.q);
     else f = truncf(__int_as_float(v) * p.q.scale);
     return FP ? (f + 0.5f) : __int_as_float(__float2int_rz(f));
+}
+
+// Calls fn(integral_constant<int, INK>) for the input kind of this launch.
+template <class Fn>
+__device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
+{
+    if (p.in_kind == DS_IN_I32) fn(std::integral_constant<int, INK_I32>());
+    else if (p.in_kind == DS_IN_I32_CLAMP) fn(std::integral_constant<int, INK_I32_CLAMP>());
+    else fn(std::integral_constant<int, INK_F32>());
 }
 
 // Warp-specialised FP32-pipe kernel (ds_gemm_ws.cu).  am: AM_LINEAR, AM_TABLE or the window

@@ -152,12 +152,12 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         const int32_t* wrow = (n0 + wn < p.N) ? p.packed + (long long)(n0 + wn) * p.dec.row_len : nullptr;
         const uint32_t fmask = (1u << p.dec.fw) - 1u;
 
-        // Gathers and stores the x tile of one k-tile.  IN32: int32 input kind; LAST: the tile may
+        // Gathers and stores the x tile of one k-tile.  INK: input kind; LAST: the tile may
         // reach past K, where x is stored as 0 (see the weight tail below).
-        auto stage_x = [&](auto in32_tag, auto last_tag, int st, int k0) {
-            constexpr bool IN32 = decltype(in32_tag)::value;
+        auto stage_x = [&](auto ink_tag, auto last_tag, int st, int k0) {
+            constexpr int INK = decltype(ink_tag)::value;
             constexpr bool LAST = decltype(last_tag)::value;
-            const int padv = IN32 ? 0 : kPadMarker;
+            const int padv = (INK != INK_F32) ? 0 : kPadMarker;
             if (ROW) {
                 // UR rows of the k-tile at a time: 2 * UR * KW loads in flight per thread
                 constexpr int UR = (KW == 1) ? 4 : (KW == 3 ? 4 : 2);
@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                         for (int q = 0; q < PIX; ++q)
 #pragma unroll
                             for (int kw = 0; kw < KW; ++kw) {
-                                float o = operand_of<true, IN32>(p, v[q][u][kw]);
+                                float o = operand_of<true, INK>(p, v[q][u][kw]);
                                 if (LAST && k0 + (r0 + u) * KW + kw >= p.K) o = 0.f;
                                 dst[(u * KW + kw) * S::AP + q * WS_PROD] = o;
                             }
@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     for (int u = 0; u < UK; ++u)
 #pragma unroll
                         for (int q = 0; q < PIX; ++q) {
-                            float o = operand_of<true, IN32>(p, v[q][u]);
+                            float o = operand_of<true, INK>(p, v[q][u]);
                             if (LAST && k0 + kb + u >= p.K) o = 0.f;
                             dst[u * S::AP + q * WS_PROD] = o;
                         }
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 #pragma unroll
                         for (int u = 0; u < UP; ++u) {
                             const int ml = mb + RP * u + (pt >> 5);
-                            float o = operand_of<true, IN32>(p, v[u]);
+                            float o = operand_of<true, INK>(p, v[u]);
                             if (LAST && k0 + kl >= p.K) o = 0.f;
                             s.a[st][kl][ml] = o;
                         }
@@ -289,12 +289,10 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             }
             if (CONV) producer_bar();
 
-            if (p.in_kind == DS_IN_I32) {
-                if (last) stage_x(std::true_type(), std::true_type(), st, k0);
-                else stage_x(std::true_type(), std::false_type(), st, k0);
-            } else {
-                stage_x(std::false_type(), std::true_type(), st, k0);
-            }
+            with_input_kind(p, [&](auto ink_tag) {
+                if (last) stage_x(ink_tag, std::true_type(), st, k0);
+                else stage_x(ink_tag, std::false_type(), st, k0);
+            });
 
             // ---- weight tile: decode through the table ------------------------------------------------
             // Slots k >= K of the last words decode like any field (a zero field is -2^0); the x

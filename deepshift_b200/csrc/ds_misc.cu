@@ -1,4 +1,6 @@
 // Weight packing, the standalone quantiser, the issue-rate probe and the status strings.
+#include <climits>
+
 #include "ds_common.cuh"
 
 namespace ds {
@@ -38,6 +40,51 @@ __global__ void quantize_kernel(const float* __restrict__ x, int32_t* __restrict
          i += (long long)gridDim.x * blockDim.x) {
         const float v = __ldg(x + i);
         out[i] = (kind == DS_IN_F32_CONV) ? __float2int_rz(quant_conv_f(v, q)) : __float2int_rz(v * q.scale);
+    }
+}
+
+// Max pooling on int32 NCHW; positions outside the image do not take part (as with
+// torch.nn.functional.max_pool2d's implicit -inf padding).  Monotone, hence identical to pooling
+// the fp32 values int / 2^F and converting back.
+__global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out, long long total, int H,
+                               int W, int OH, int OW, int k, int st, int pad)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int ow = int(i % OW);
+        const long long r = i / OW;
+        const int oh = int(r % OH);
+        const long long bc = r / OH;
+        const int32_t* src = x + bc * H * W;
+        int best = INT_MIN;
+        for (int kh = 0; kh < k; ++kh) {
+            const int ih = oh * st - pad + kh;
+            if (unsigned(ih) >= unsigned(H)) continue;
+            for (int kw = 0; kw < k; ++kw) {
+                const int iw = ow * st - pad + kw;
+                if (unsigned(iw) < unsigned(W)) best = max(best, __ldg(src + ih * W + iw));
+            }
+        }
+        out[i] = best;
+    }
+}
+
+// Global average pooling of int32 fixed-point planes followed by the LinearShift entry
+// conversion: one warp per (b, c) plane sums the codes exactly (int64), then
+// mean = float(sum) * 2^-F / (H*W) in fp32 and out = trunc(mean * 2^F).
+__global__ void avgpool_fix_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out, int planes, int hw,
+                                   float inv_scale, float scale)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= planes) return;
+    const int32_t* src = x + (long long)warp * hw;
+    long long sum = 0;
+    for (int i = lane; i < hw; i += 32) sum += __ldg(src + i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) {
+        const float mean = __fdiv_rn(__ll2float_rn(sum) * inv_scale, float(hw));
+        out[warp] = __float2int_rz(mean * scale);
     }
 }
 
@@ -212,6 +259,37 @@ extern "C" int ds_quantize_f32(const float* x, int32_t* out, long long n, int ki
     const long long want = (n + threads - 1) / threads;
     const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
     quantize_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, n, kind, q);
+    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
+extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, int H, int W, int k, int stride,
+                                int pad, void* stream)
+{
+    if (!x || !out || B < 0 || C <= 0 || H <= 0 || W <= 0 || k <= 0 || stride <= 0 || pad < 0 || 2 * pad > k)
+        return DS_ERR_BAD_ARG;
+    if (H + 2 * pad < k || W + 2 * pad < k) return DS_ERR_BAD_ARG;
+    const int OH = (H + 2 * pad - k) / stride + 1, OW = (W + 2 * pad - k) / stride + 1;
+    const long long total = (long long)B * C * OH * OW;
+    if (total == 0) return DS_OK;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
+    maxpool_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, total, H, W, OH, OW, k,
+                                                                            stride, pad);
+    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
+extern "C" int ds_avgpool_fix_i32(const int32_t* x, int32_t* out, int B, int C, int H, int W, int F, void* stream)
+{
+    if (!x || !out || B < 0 || C <= 0 || H <= 0 || W <= 0 || F < 0 || F > 30) return DS_ERR_BAD_ARG;
+    const long long planes = (long long)B * C;
+    if (planes == 0) return DS_OK;
+    if (planes > 2147483647LL / 32) return DS_ERR_RANGE;
+    const int threads = 256;
+    const int blocks = int((planes * 32 + threads - 1) / threads);
+    const float scale = float(1ll << F);
+    avgpool_fix_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, int(planes), H * W,
+                                                                                1.0f / scale, scale);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

@@ -46,13 +46,14 @@ def _no_cpu():
 
 
 def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=False, requant=False,
-          residual=None, act_bits=0):
+          residual=None, act_bits=0, round_f32=False):
     f = _ffi.Fuse()
     f.in_kind, f.out_kind = in_kind, out_kind
     f.act_integer_bits, f.act_fraction_bits = int(act_integer_bits), int(act_fraction_bits)
     f.relu, f.requant = int(bool(relu)), int(bool(requant))
     f.residual = residual.data_ptr() if residual is not None else None
     f.act_bits = int(act_bits)
+    f.round_f32 = int(bool(round_f32))
     return f
 
 
@@ -131,12 +132,13 @@ def compress_sign_and_shift(shift, sign, comp_size, base, bits, row_length, num)
 
 def linear_fused(input, out_features, bias_i32, conc_weight, *, in_kind=_ffi.IN_I32, out_kind=_ffi.OUT_I32,
                  act_integer_bits=16, act_fraction_bits=16, relu=False, requant=False, residual=None,
-                 act_bits=0):
-    _check_tensor(input, "input", torch.int32 if in_kind == _ffi.IN_I32 else torch.float32)
+                 act_bits=0, round_f32=False, out=None):
+    _check_tensor(input, "input", torch.int32 if in_kind in (_ffi.IN_I32, _ffi.IN_I32_CLAMP) else torch.float32)
     M, K = input.shape
-    out = torch.empty([M, out_features], device=input.device,
-                      dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
-    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits)
+    if out is None:
+        out = torch.empty([M, out_features], device=input.device,
+                          dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
+    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32)
     with torch.cuda.device(input.device):
         rc = _ffi.lib().ds_linear_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),
@@ -148,8 +150,8 @@ def linear_fused(input, out_features, bias_i32, conc_weight, *, in_kind=_ffi.IN_
 
 def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0, *, in_kind=_ffi.IN_I32,
                  out_kind=_ffi.OUT_I32, act_integer_bits=16, act_fraction_bits=16, relu=False, requant=False,
-                 residual=None, act_bits=0):
-    _check_tensor(input, "input", torch.int32 if in_kind == _ffi.IN_I32 else torch.float32)
+                 residual=None, act_bits=0, round_f32=False, out=None):
+    _check_tensor(input, "input", torch.int32 if in_kind in (_ffi.IN_I32, _ffi.IN_I32_CLAMP) else torch.float32)
     sh, sw = _pair(stride)
     ph, pw = _pair(padding)
     B, C, H, W = input.shape
@@ -157,13 +159,14 @@ def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0
     if C2 != C:
         raise RuntimeError("input has %d channels, weight expects %d" % (C, C2))
     OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
-    out = torch.empty([B, OC, OH, OW], device=input.device,
-                      dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
+    if out is None:
+        out = torch.empty([B, OC, OH, OW], device=input.device,
+                          dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
     if residual is not None:
         _check_tensor(residual, "residual", torch.int32)
         if residual.shape != out.shape:
             raise RuntimeError("residual shape %s != output shape %s" % (tuple(residual.shape), tuple(out.shape)))
-    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits)
+    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32)
     with torch.cuda.device(input.device):
         rc = _ffi.lib().ds_conv2d_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),
@@ -182,6 +185,36 @@ def quantize(input, act_integer_bits, act_fraction_bits, like_conv=True):
                                         _ffi.IN_F32_CONV if like_conv else _ffi.IN_F32_LINEAR,
                                         act_integer_bits, act_fraction_bits, _stream_ptr(input.device))
     _ffi.check(rc, "quantize")
+    return out
+
+
+def maxpool2d_i32(input, kernel_size, stride, padding=0, out=None):
+    """Max pooling of int32 fixed-point NCHW activations (exact counterpart of F.max_pool2d on
+    the fp32 values)."""
+    _check_tensor(input, "input", torch.int32)
+    B, C, H, W = input.shape
+    OH = (H + 2 * padding - kernel_size) // stride + 1
+    OW = (W + 2 * padding - kernel_size) // stride + 1
+    if out is None:
+        out = torch.empty([B, C, OH, OW], dtype=torch.int32, device=input.device)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_maxpool2d_i32(input.data_ptr(), out.data_ptr(), B, C, H, W, kernel_size, stride,
+                                         padding, _stream_ptr(input.device))
+    _ffi.check(rc, "maxpool2d_i32")
+    return out
+
+
+def avgpool_fix_i32(input, act_fraction_bits, out=None):
+    """Global average pooling of int32 activations followed by the LinearShift entry conversion;
+    returns int32 [B, C]."""
+    _check_tensor(input, "input", torch.int32)
+    B, C, H, W = input.shape
+    if out is None:
+        out = torch.empty([B, C], dtype=torch.int32, device=input.device)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_avgpool_fix_i32(input.data_ptr(), out.data_ptr(), B, C, H, W, act_fraction_bits,
+                                           _stream_ptr(input.device))
+    _ffi.check(rc, "avgpool_fix_i32")
     return out
 
 

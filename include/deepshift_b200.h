@@ -45,7 +45,10 @@ typedef enum {
 enum {
     DS_IN_I32 = 0,       /* int32 fixed point (what the reference kernels receive)                         */
     DS_IN_F32_CONV = 1,  /* fp32, quantised in the kernel as Conv2dShift does: clamp(floor(x*2^F)) -- utils.py:7-21, modules.py:153,317 */
-    DS_IN_F32_LINEAR = 2 /* fp32, quantised as LinearShift does: trunc(x*2^F), no clamp -- modules.py:25 */
+    DS_IN_F32_LINEAR = 2,/* fp32, quantised as LinearShift does: trunc(x*2^F), no clamp -- modules.py:25 */
+    DS_IN_I32_CLAMP = 3  /* int32 fixed point, clamped on read to [-2^(I-1+F), (2^(I-1)-1)*2^F]: what
+                            Conv2dShift's round_to_fixed does to a value already on the 2^-F grid.
+                            Lets one unclamped tensor feed both a convolution and a residual add. */
 };
 
 /* Output element kinds of the *_ex entry points. */
@@ -57,7 +60,7 @@ enum {
 /*
  * Optional fused prologue/epilogue of ds_linear_ex / ds_conv2d_ex.  Zero-initialise for the
  * plain int32-in / int32-out behaviour.  Order of the epilogue on v = acc + bias:
- *   residual add -> ReLU -> requantise clamp -> store.
+ *   residual add -> ReLU -> requantise clamp -> fp32 rounding -> store.
  */
 typedef struct {
     int in_kind;            /* DS_IN_*                                                     */
@@ -71,8 +74,12 @@ typedef struct {
     int act_bits;           /* caller's guarantee on int32 inputs: every x satisfies
                                -2^(act_bits-1) <= x <= 2^(act_bits-1).  0 = no guarantee
                                (exact integer path).  1..20 enables the FP32-pipe path.
-                               Implied by DS_IN_F32_CONV (I+F).                            */
-    int reserved[4];
+                               Implied by DS_IN_F32_CONV and
+                               DS_IN_I32_CLAMP (I+F).                            */
+    int round_f32;          /* v = int(float(v)): the rounding the reference's `out.float()` applies
+                               to sums beyond 2^24, so that an int32 tensor handed to the next layer
+                               holds exactly the value the reference's fp32 tensor would        */
+    int reserved[3];
 } ds_fuse_t;
 
 /*
@@ -119,6 +126,19 @@ int ds_compress(const int32_t *shiftp, const int32_t *sign, int32_t *packed, int
  */
 int ds_quantize_f32(const float *x, int32_t *out, long long n, int kind, int act_integer_bits,
                     int act_fraction_bits, void *stream);
+
+/*
+ * Inter-layer glue of the integer pipeline (no counterpart in the reference's native code, which
+ * leaves these steps to torch ops on fp32: F.max_pool2d / adaptive_avg_pool2d in the model
+ * definitions, e.g. torchvision ResNet).  Both are exact restatements on the int32 codes.
+ *   ds_maxpool2d_i32   : square window k, stride, symmetric pad; out [B,C,OH,OW].
+ *   ds_avgpool_fix_i32 : global average over H*W, then the LinearShift entry conversion
+ *                        trunc(mean * 2^F) (modules.py:25); out [B,C] int32.  mean is
+ *                        float(exact integer sum) / 2^F / (H*W) in fp32.
+ */
+int ds_maxpool2d_i32(const int32_t *x, int32_t *out, int B, int C, int H, int W, int k, int stride,
+                     int pad, void *stream);
+int ds_avgpool_fix_i32(const int32_t *x, int32_t *out, int B, int C, int H, int W, int F, void *stream);
 
 /*
  * Register-only issue-rate probe used for the roofline denominator.
