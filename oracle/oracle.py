@@ -80,6 +80,7 @@ def linear(x, shift, sign, bias=None):
 def pad_nchw(x, ph, pw):
     x = _i32(x)
     B, C, H, W = x.shape
+    ph, pw = int(ph), int(pw)
     xp = np.empty((B, C, H + 2 * ph, W + 2 * pw), dtype=np.int32)
     lib().dso_pad_nchw(_p(x), _p(xp), B, C, H, W, ph, pw)
     return xp
@@ -93,8 +94,8 @@ def conv2d(x, shift, sign, bias=None, stride=(1, 1), padding=(0, 0), zero_sign_a
     the default is the canonical rule of the linear kernel (sign 0 contributes nothing).
     """
     x, shift, sign, bias = _i32(x), _i32(shift), _i32(sign), _i32(bias)
-    sh, sw = stride
-    ph, pw = padding
+    sh, sw = int(stride[0]), int(stride[1])
+    ph, pw = int(padding[0]), int(padding[1])
     xp = pad_nchw(x, ph, pw) if (ph or pw) else x
     B, C, Hp, Wp = xp.shape
     OC, C2, KH, KW = shift.shape
@@ -109,7 +110,7 @@ def conv2d(x, shift, sign, bias=None, stride=(1, 1), padding=(0, 0), zero_sign_a
 def im2col(xp, KH, KW, stride=(1, 1)):
     xp = _i32(xp)
     B, C, Hp, Wp = xp.shape
-    sh, sw = stride
+    sh, sw = int(stride[0]), int(stride[1])
     OH, OW = (Hp - KH) // sh + 1, (Wp - KW) // sw + 1
     col = np.empty((B * OH * OW, C * KH * KW), dtype=np.int32)
     lib().dso_im2col(_p(xp), _p(col), B, C, Hp, Wp, KH, KW, sh, sw)
@@ -128,6 +129,7 @@ def conv2d_via_gemm(x, shift, sign, bias=None, stride=(1, 1), padding=(0, 0)):
     evaluated with the linear kernel's arithmetic.  Used to cross-check ``conv2d``."""
     x, shift = _i32(x), _i32(shift)
     OC, C, KH, KW = shift.shape
+    stride = (int(stride[0]), int(stride[1]))
     xp = pad_nchw(x, *padding) if (padding[0] or padding[1]) else x
     B, _, Hp, Wp = xp.shape
     OH, OW = (Hp - KH) // stride[0] + 1, (Wp - KW) // stride[1] + 1

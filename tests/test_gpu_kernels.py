@@ -1,0 +1,304 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the Python operator layer and the
+C ABI.  Integer results must be bit-identical; fp32 results are exact conversions of them, so
+they are compared with array_equal as well."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import acts_q16, acts_wide, weights
+
+pytestmark = pytest.mark.gpu
+
+
+def _cw(shift, sign, dev):
+    from deepshift_b200 import utils
+    return utils.compress_bits(torch.from_numpy(shift).float(), torch.from_numpy(sign).float(), device=dev)
+
+
+def _t(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+# ----------------------------------------------------------------------------------------- packing
+@pytest.mark.parametrize("lo,zeros", [(-1, False), (-3, False), (-7, False), (-15, False), (-15, True), (-31, True)])
+@pytest.mark.parametrize("K", [1, 5, 16, 131])
+def test_compress_matches_oracle(oracle, cuda_device, lo, zeros, K):
+    rng = np.random.default_rng(K - lo)
+    shift, sign = weights(rng, (7, K), lo, zeros)
+    cw = _cw(shift, sign, cuda_device)
+    packed, base, bits = oracle.compress_bits(shift, sign)
+    assert (cw.base, cw.bits) == (base, bits)
+    assert np.array_equal(cw.data.cpu().numpy().reshape(packed.shape), packed)
+
+
+def test_compress_api_matches_reference_signature(oracle, cuda_device):
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(3)
+    shiftp = rng.integers(0, 16, (4, 3, 3, 3)).astype(np.int32)
+    sign = rng.choice([-1, 1], (4, 3, 3, 3)).astype(np.int32)
+    bits, num = 4, 6
+    row = (27 + num - 1) // num
+    out = kernels.compress_sign_and_shift(_t(shiftp, cuda_device), _t(sign, cuda_device), 4 * row, 0, bits, row, num)
+    assert out.dtype == torch.int32 and out.shape == (4 * row,)
+    assert np.array_equal(out.cpu().numpy().reshape(4, row), oracle.compress(shiftp.reshape(4, -1), sign.reshape(4, -1), bits, 0))
+    with pytest.raises(RuntimeError, match="inconsistent"):
+        kernels.compress_sign_and_shift(_t(shiftp, cuda_device), _t(sign, cuda_device), 4 * row, 0, bits, row + 1, num)
+
+
+# ----------------------------------------------------------------------------------------- linear
+LINEAR_SHAPES = [(1, 1, 1), (3, 7, 5), (64, 784, 512), (130, 131, 129), (257, 500, 10), (64, 512, 10), (200, 96, 70),
+                 (1000, 300, 40), (1, 4096, 33), (513, 29, 260)]
+
+
+@pytest.mark.parametrize("M,K,N", LINEAR_SHAPES)
+@pytest.mark.parametrize("act_bits", [0, 16])
+def test_linear_matches_oracle(oracle, cuda_device, M, K, N, act_bits):
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(M * 7 + K * 3 + N)
+    x = acts_q16(rng, (M, K))
+    shift, sign = weights(rng, (N, K))
+    bias = rng.integers(-2000, 2000, N).astype(np.int32)
+    out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                         _cw(shift, sign, cuda_device), act_bits=act_bits)
+    assert out.dtype == torch.int32 and tuple(out.shape) == (M, N)
+    assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, bias))
+
+
+@pytest.mark.parametrize("lo,zeros", [(-1, False), (-3, False), (-7, False), (-15, False), (-31, True), (-15, True)])
+@pytest.mark.parametrize("act_bits", [0, 16])
+def test_linear_every_field_width(oracle, cuda_device, lo, zeros, act_bits):
+    """bits = 1..6, i.e. 16, 10, 8, 6, 5 and 4 weights per word, ragged K."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(-lo * 13 + act_bits)
+    M, K, N = 70, 203, 37
+    x = acts_q16(rng, (M, K))
+    shift, sign = weights(rng, (N, K), lo, zeros)
+    cw = _cw(shift, sign, cuda_device)
+    out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, None, cw, act_bits=act_bits)
+    assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, None))
+
+
+def test_linear_golden_vectors_of_the_reference(oracle, cuda_device, golden_dir):
+    from deepshift_b200 import kernels
+    g = np.load(os.path.join(golden_dir, "linear_ref.npz"))
+    for i in range(int(g["n"])):
+        x, shift, sign, bias = g[f"x{i}"], g[f"shift{i}"], g[f"sign{i}"], g[f"bias{i}"]
+        out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                             _cw(shift, sign, cuda_device))
+        assert np.array_equal(out.cpu().numpy(), g[f"y{i}"]), i
+
+
+def test_linear_wide_inputs_wrap_like_the_reference(oracle, cuda_device):
+    """Unbounded int32 activations take the integer path; sums wrap modulo 2^32."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(8)
+    x = acts_wide(rng, (33, 300), 30)
+    shift, sign = weights(rng, (17, 300), -3, zeros=False)
+    out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, None, _cw(shift, sign, cuda_device))
+    assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, None))
+
+
+def test_linear_left_shifts(oracle, cuda_device):
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(9)
+    x = acts_wide(rng, (20, 50), 12)
+    shift = rng.integers(-6, 4, (9, 50)).astype(np.int32)
+    sign = rng.choice([-1, 0, 1], (9, 50)).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    assert cw.base < 0
+    out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, None, cw, act_bits=16)  # hint ignored: base != 0
+    assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, None))
+
+
+def test_linear_empty_batch_and_errors(cuda_device):
+    from deepshift_b200 import kernels, utils
+    rng = np.random.default_rng(1)
+    shift, sign = weights(rng, (4, 8))
+    cw = _cw(shift, sign, cuda_device)
+    out = kernels.linear(torch.zeros((0, 8), dtype=torch.int32, device=cuda_device), _t(shift, cuda_device), None, None, cw)
+    assert tuple(out.shape) == (0, 4)
+    with pytest.raises(RuntimeError, match="must be torch.int32"):
+        kernels.linear(torch.zeros((2, 8), device=cuda_device), _t(shift, cuda_device), None, None, cw)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        kernels.linear(torch.zeros((8, 2), dtype=torch.int32, device=cuda_device).t(), _t(shift, cuda_device), None, None, cw)
+    bad = utils.ConcWeight(cw.data, 0, 9)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        kernels.linear(torch.zeros((2, 8), dtype=torch.int32, device=cuda_device), _t(shift, cuda_device), None, None, bad)
+
+
+# ----------------------------------------------------------------------------------------- convolution
+CONV_CASES = [  # B, C, H, W, OC, KH, KW, stride, pad, zeros
+    (2, 3, 8, 8, 4, 3, 3, (1, 1), (1, 1), True), (2, 4, 9, 7, 5, 3, 3, (2, 2), (1, 1), True),
+    (3, 1, 28, 28, 20, 5, 5, (1, 1), (0, 0), True), (2, 3, 30, 30, 64, 7, 7, (2, 2), (3, 3), True),
+    (3, 64, 14, 14, 128, 1, 1, (2, 2), (0, 0), False), (4, 64, 7, 7, 64, 3, 3, (1, 1), (1, 1), True),
+    (2, 16, 12, 12, 33, 3, 3, (1, 1), (1, 1), True), (5, 32, 8, 8, 130, 3, 3, (1, 1), (1, 1), True),
+    (2, 5, 9, 11, 7, 2, 4, (1, 2), (1, 0), True), (1, 3, 6, 6, 3, 6, 6, (1, 1), (0, 0), True),
+    (2, 20, 12, 12, 50, 5, 5, (1, 1), (0, 0), True), (300, 2, 5, 5, 3, 3, 3, (1, 1), (1, 1), True),
+    (2, 3, 13, 13, 8, 9, 9, (2, 2), (4, 4), True),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=lambda c: "x".join(str(v) for v in c[:7]))
+@pytest.mark.parametrize("act_bits", [0, 16])
+def test_conv_matches_oracle(oracle, cuda_device, case, act_bits):
+    from deepshift_b200 import kernels
+    B, C, H, W, OC, KH, KW, st, pad, zeros = case
+    rng = np.random.default_rng(B * 31 + C * 17 + OC)
+    x = acts_q16(rng, (B, C, H, W))
+    shift, sign = weights(rng, (OC, C, KH, KW), -15, zeros)
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                         _cw(shift, sign, cuda_device), st, pad, act_bits=act_bits)
+    ref = oracle.conv2d(x, shift, sign, bias, st, pad)
+    assert tuple(out.shape) == ref.shape
+    assert np.array_equal(out.cpu().numpy(), ref)
+
+
+def test_conv_golden_vectors_of_the_reference(cuda_device, golden_dir):
+    """Zero-free cases equal the reference's CPU convolution output verbatim."""
+    from deepshift_b200 import kernels
+    g = np.load(os.path.join(golden_dir, "conv_ref.npz"))
+    checked = 0
+    for i in range(int(g["n"])):
+        if (g[f"sign{i}"] == 0).any():
+            continue
+        x, shift, sign, bias = g[f"x{i}"], g[f"shift{i}"], g[f"sign{i}"], g[f"bias{i}"]
+        out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                             _cw(shift, sign, cuda_device), tuple(int(v) for v in g[f"stride{i}"]),
+                             tuple(int(v) for v in g[f"pad{i}"]), act_bits=16)
+        assert np.array_equal(out.cpu().numpy(), g[f"y{i}"]), i
+        checked += 1
+    assert checked >= 5
+
+
+def test_conv_rejects_dilation_and_groups(cuda_device):
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(2)
+    shift, sign = weights(rng, (4, 2, 3, 3))
+    cw = _cw(shift, sign, cuda_device)
+    x = torch.zeros((1, 2, 6, 6), dtype=torch.int32, device=cuda_device)
+    with pytest.raises(RuntimeError, match="dilation"):
+        kernels.conv2d(x, _t(shift, cuda_device), None, None, cw, 1, 0, dilation=2)
+    with pytest.raises(RuntimeError, match="dilation"):
+        kernels.conv2d(x, _t(shift, cuda_device), None, None, cw, 1, 0, groups=2)
+
+
+# ----------------------------------------------------------------------------------------- fused forms
+@pytest.mark.parametrize("shape", [(2, 8, 12, 12, 16, 3, 1, 1), (3, 16, 9, 9, 140, 3, 2, 1), (2, 6, 10, 10, 70, 1, 1, 0)])
+def test_conv_fused_epilogues(oracle, cuda_device, shape):
+    from deepshift_b200 import _ffi, kernels
+    B, C, H, OC, k, s, p = shape[0], shape[1], shape[2], shape[4], shape[5], shape[6], shape[7]
+    I, F = 4, 12
+    rng = np.random.default_rng(sum(shape))
+    xf = rng.normal(0, 3, (B, C, H, H)).astype(np.float32)
+    shift, sign = weights(rng, (OC, C, k, k))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    xi = oracle.to_fixed_conv(xf, I, F)
+    ref = oracle.conv2d(xi, shift, sign, bias, (s, s), (p, p))
+    wshape = (OC, C, k, k)
+    # fp32 in (quantised in the kernel), fp32 out
+    out = kernels.conv2d_fused(_t(xf, cuda_device), wshape, _t(bias, cuda_device), cw, s, p, in_kind=_ffi.IN_F32_CONV,
+                               out_kind=_ffi.OUT_F32, act_integer_bits=I, act_fraction_bits=F)
+    assert np.array_equal(out.cpu().numpy(), oracle.from_fixed(ref, F))
+    # unclamped int32 in, clamped on read; residual + ReLU + fp32 rounding in the epilogue
+    wide = (xi.astype(np.int64) * 3).astype(np.int32)
+    res = rng.integers(-50000, 50000, ref.shape).astype(np.int32)
+    lo, hi = -(1 << (I - 1 + F)), ((1 << (I - 1)) - 1) << F
+    ref2 = oracle.conv2d(np.clip(wide, lo, hi), shift, sign, bias, (s, s), (p, p))
+    ref2 = np.maximum(ref2.astype(np.float32) + res.astype(np.float32), 0).astype(np.int64).astype(np.int32)
+    out = kernels.conv2d_fused(_t(wide, cuda_device), wshape, _t(bias, cuda_device), cw, s, p,
+                               in_kind=_ffi.IN_I32_CLAMP, act_integer_bits=I, act_fraction_bits=F, relu=True,
+                               residual=_t(res, cuda_device), round_f32=True)
+    assert np.array_equal(out.cpu().numpy(), ref2)
+    # requantise clamp on write
+    out = kernels.conv2d_fused(_t(xi, cuda_device), wshape, _t(bias, cuda_device), cw, s, p, act_bits=16,
+                               act_integer_bits=I, act_fraction_bits=F, relu=True, requant=True)
+    assert np.array_equal(out.cpu().numpy(), np.clip(np.maximum(ref, 0), lo, hi))
+
+
+def test_linear_fused_fp32(oracle, cuda_device):
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(4)
+    xf = rng.normal(0, 2, (37, 90)).astype(np.float32)
+    shift, sign = weights(rng, (21, 90))
+    bias = rng.integers(-2000, 2000, 21).astype(np.int32)
+    ref = oracle.linear(oracle.to_fixed_linear(xf, 12), shift, sign, bias)
+    out = kernels.linear_fused(_t(xf, cuda_device), 21, _t(bias, cuda_device), _cw(shift, sign, cuda_device),
+                               in_kind=_ffi.IN_F32_LINEAR, out_kind=_ffi.OUT_F32, act_fraction_bits=12, relu=True)
+    assert np.array_equal(out.cpu().numpy(), oracle.from_fixed(np.maximum(ref, 0), 12))
+
+
+def test_quantize_matches_round_to_fixed(oracle, cuda_device):
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(6)
+    v = np.concatenate([rng.normal(0, 4, 5000), [7.5, 6.99999, -9.0, 7.0, -8.0, 0.0, 1e-9, -1e-9]]).astype(np.float32)
+    for I, F in [(4, 12), (8, 8), (2, 3), (1, 7)]:
+        got = kernels.quantize(_t(v, cuda_device), I, F, like_conv=True).cpu().numpy()
+        assert np.array_equal(got, oracle.to_fixed_conv(v, I, F)), (I, F)
+    got = kernels.quantize(_t(v, cuda_device), 4, 12, like_conv=False).cpu().numpy()
+    assert np.array_equal(got, oracle.to_fixed_linear(v, 12))
+
+
+def test_pooling_on_codes(cuda_device):
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(7)
+    x = rng.integers(-40000, 40000, (3, 5, 13, 13)).astype(np.int32)
+    xt = _t(x, cuda_device)
+    for k, s, p in [(2, 2, 0), (3, 2, 1)]:
+        ref = torch.nn.functional.max_pool2d(xt.double(), k, s, p).to(torch.int32)
+        assert torch.equal(kernels.maxpool2d_i32(xt, k, s, p), ref)
+    F = 12
+    got = kernels.avgpool_fix_i32(xt, F).cpu().numpy()
+    mean = (x.astype(np.int64).sum(axis=(2, 3)).astype(np.float32) / np.float32(1 << F)) / np.float32(169)
+    assert np.array_equal(got, np.trunc(mean.astype(np.float32) * np.float32(1 << F)).astype(np.int32))
+
+
+# ----------------------------------------------------------------------------------------- modules
+def test_modules_match_reference_golden_forward(cuda_device, golden_dir):
+    """LinearShift / Conv2dShift with use_kernel=True reproduce the fp32 outputs recorded from the
+    reference's own modules (use_cuda=False there)."""
+    from deepshift_b200 import modules
+    g = np.load(os.path.join(golden_dir, "glue_ref.npz"))
+    lin = modules.LinearShift(40, 12, use_kernel=True, act_integer_bits=4, act_fraction_bits=12).to(cuda_device)
+    lin.shift.data, lin.sign.data, lin.bias.data = (_t(g["lin_shift"], cuda_device), _t(g["lin_sign"], cuda_device),
+                                                    _t(g["lin_bias"], cuda_device))
+    assert np.array_equal(lin(_t(g["lin_x"], cuda_device)).cpu().numpy(), g["lin_y"])
+    conv = modules.Conv2dShift(3, 6, 3, use_kernel=True, act_integer_bits=4, act_fraction_bits=12).to(cuda_device)
+    conv.shift.data, conv.sign.data, conv.bias.data = (_t(g["conv_shift"], cuda_device), _t(g["conv_sign"], cuda_device),
+                                                       _t(g["conv_bias"], cuda_device))
+    assert np.array_equal(conv(_t(g["conv_x"], cuda_device)).cpu().numpy(), g["conv_y"])
+
+
+def test_convert_to_shift_use_kernel_end_to_end(oracle, cuda_device):
+    import torch.nn as nn
+    from deepshift_b200 import convert, modules
+    torch.manual_seed(3)
+    model = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(), nn.MaxPool2d(2), nn.Flatten(), nn.Linear(8 * 16, 10))
+    model, n = convert.convert_to_shift(model, 1000, 'PS', convert_weights=True, use_kernel=True,
+                                        act_integer_bits=4, act_fraction_bits=12)
+    model = convert.round_shift_weights(model.to(cuda_device), act_integer_bits=4, act_fraction_bits=12)
+    assert n == 1 and isinstance(model[0], modules.Conv2dShift) and model[0].conc_weight is not None
+    x = torch.randn(5, 3, 8, 8)
+    y = model(x.to(cuda_device)).cpu().numpy()
+    c, l = model[0], model[4]
+    I, F = 4, 12
+    ci = oracle.conv2d(oracle.to_fixed_conv(x.numpy(), I, F), c.shift.data.cpu().numpy().astype(np.int32),
+                       c.sign.data.cpu().numpy().astype(np.int32), oracle.to_fixed_conv(c.bias.data.cpu().numpy(), I, F),
+                       (1, 1), (1, 1))
+    h = np.maximum(oracle.from_fixed(ci, F), 0)
+    h = torch.nn.functional.max_pool2d(torch.from_numpy(h), 2).flatten(1).numpy()
+    li = oracle.linear(oracle.to_fixed_linear(h, F), l.shift.data.cpu().numpy().astype(np.int32),
+                       l.sign.data.cpu().numpy().astype(np.int32), oracle.to_fixed_linear(l.bias.data.cpu().numpy(), F))
+    assert np.array_equal(y, oracle.from_fixed(li, F))
+
+
+def test_no_kernel_wait_ran_out(cuda_device):
+    """The warp-specialised kernel's bounded waits never give up in a correct run."""
+    from deepshift_b200 import _ffi
+    flag = ctypes.c_int(-1)
+    assert _ffi.lib().ds_last_kernel_error(ctypes.byref(flag)) == 0
+    assert flag.value == 0

@@ -1,0 +1,203 @@
+"""Host logic that needs no GPU: helpers with the reference's names, conversion, workload
+descriptions, and the C ABI's symbol table and argument checks."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_round_to_fixed_and_shift_sign_match_reference_golden(golden_dir):
+    from deepshift_b200 import utils
+    g = np.load(os.path.join(golden_dir, "glue_ref.npz"))
+    v = torch.from_numpy(g["rtf_in"])
+    for I, F in [(4, 12), (16, 16), (8, 8), (1, 7), (2, 3)]:
+        assert np.array_equal(utils.round_to_fixed(v, I, F).numpy(), g[f"rtf_{I}_{F}"]), (I, F)
+    shift, sign = utils.get_shift_and_sign(torch.from_numpy(g["gss_w"]))
+    assert np.array_equal(sign.numpy(), g["gss_sign"])
+    nz = g["gss_w"] != 0
+    assert np.array_equal(shift.numpy()[nz], g["gss_shift"][nz])
+
+
+def test_round_accepts_the_reference_spelling():
+    from deepshift_b200 import utils
+    x = torch.tensor([0.4, 1.5, -2.5])
+    assert torch.equal(utils.round(x, 'determinstic'), utils.round(x, 'deterministic'))
+    with pytest.raises(AssertionError):
+        utils.round(x, 'nearest')
+
+
+def test_module_signatures_match_reference():
+    import inspect
+    from deepshift_b200 import convert, kernels, modules
+    lin = inspect.signature(modules.LinearShift.__init__)
+    assert list(lin.parameters)[1:] == ['in_features', 'out_features', 'bias', 'check_grad', 'freeze_sign', 'use_kernel',
+                                        'use_cuda', 'rounding', 'weight_bits', 'act_integer_bits', 'act_fraction_bits']
+    conv = inspect.signature(modules.Conv2dShift.__init__)
+    assert list(conv.parameters)[1:] == ['in_channels', 'out_channels', 'kernel_size', 'stride', 'padding', 'dilation',
+                                         'groups', 'bias', 'padding_mode', 'check_grad', 'freeze_sign', 'use_kernel',
+                                         'use_cuda', 'rounding', 'weight_bits', 'act_integer_bits', 'act_fraction_bits']
+    assert conv.parameters['rounding'].default == 'determinstic'
+    cts = inspect.signature(convert.convert_to_shift)
+    assert list(cts.parameters) == ['model', 'shift_depth', 'shift_type', 'convert_all_linear', 'convert_weights',
+                                    'freeze_sign', 'use_kernel', 'use_cuda', 'rounding', 'weight_bits',
+                                    'act_integer_bits', 'act_fraction_bits']
+    assert list(inspect.signature(kernels.linear).parameters)[:6] == ['input', 'shift', 'sign', 'bias', 'conc_weight',
+                                                                       'use_cuda']
+    assert list(inspect.signature(kernels.conv2d).parameters)[:10] == ['input', 'shift', 'sign', 'bias', 'conc_weight',
+                                                                        'stride', 'padding', 'dilation', 'groups',
+                                                                        'use_cuda']
+    assert list(inspect.signature(kernels.compress_sign_and_shift).parameters) == ['shift', 'sign', 'comp_size', 'base',
+                                                                                   'bits', 'row_length', 'num']
+
+
+def test_convert_to_shift_structure_and_count():
+    from deepshift_b200 import convert, modules
+    model = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(),
+                          nn.Sequential(nn.Conv2d(8, 8, 3, stride=2), nn.ReLU()), nn.Flatten(), nn.Linear(8, 4))
+    model, count = convert.convert_to_shift(model, 1000, 'PS', convert_weights=True)
+    assert count == 2  # convolutions only, as the reference counts with convert_all_linear=True
+    assert convert.count_layer_type(model, modules.Conv2dShift) == 2
+    assert convert.count_layer_type(model, modules.LinearShift) == 1
+    c = model[0]
+    assert c.stride == (1, 1) and c.padding == (1, 1) and c.shift.shape == (8, 3, 3, 3)
+    assert c.shift_range == (-14, 0)
+    assert torch.all(c.sign.data.abs() <= 1)
+    # depth 1 converts the LAST convolution (the reference walks the children backwards)
+    m2 = nn.Sequential(nn.Conv2d(3, 8, 3), nn.Conv2d(8, 8, 3))
+    m2, n = convert.convert_to_shift(m2, 1, 'PS')
+    assert n == 1 and type(m2[1]) is modules.Conv2dShift and type(m2[0]) is nn.Conv2d
+    with pytest.raises(NotImplementedError):
+        convert.convert_to_shift(nn.Sequential(nn.Linear(2, 2)), 1, 'Q')
+    with pytest.raises(ValueError):
+        convert.convert_to_shift(nn.Sequential(nn.Linear(2, 2)), 1, 'XYZ')
+
+
+def test_round_shift_weights_rounds_parameters():
+    from deepshift_b200 import convert, modules
+    m = nn.Sequential(modules.LinearShift(6, 3, act_integer_bits=4, act_fraction_bits=12))
+    m[0].shift.data.fill_(-2.4)
+    m[0].sign.data.fill_(0.7)
+    m[0].bias.data.fill_(0.12345)
+    convert.round_shift_weights(m, act_integer_bits=4, act_fraction_bits=12)
+    assert torch.all(m[0].shift.data == -2) and torch.all(m[0].sign.data == 1)
+    assert torch.all(m[0].bias.data == np.floor(0.12345 * 4096) / 4096)
+
+
+def test_float_path_forward_equals_dense_layers():
+    """use_kernel=False: the layers are plain conv / linear with weights sign * 2^shift."""
+    from deepshift_b200 import modules
+    torch.manual_seed(0)
+    conv = modules.Conv2dShift(3, 4, 3, padding=1, rounding='deterministic', act_integer_bits=8, act_fraction_bits=8)
+    conv.shift.data = torch.randint(-6, 1, conv.shift.shape).float()
+    conv.sign.data = torch.randint(-1, 2, conv.sign.shape).float()
+    x = torch.randn(2, 3, 5, 5)
+    from deepshift_b200 import utils
+    w = (2.0 ** conv.shift.data) * conv.sign.data
+    ref = torch.nn.functional.conv2d(utils.round_to_fixed(x, 8, 8), w, utils.round_to_fixed(conv.bias.data, 8, 8),
+                                     padding=1)
+    assert torch.equal(conv(x), ref)
+    lin = modules.LinearShift(7, 3)
+    lin.shift.data = torch.randint(-6, 1, lin.shift.shape).float()
+    lin.sign.data = torch.randint(-1, 2, lin.sign.shape).float()
+    x = torch.randn(4, 7)
+    assert torch.equal(lin(x), torch.nn.functional.linear(x, (2.0 ** lin.shift.data) * lin.sign.data, lin.bias))
+
+
+def test_kernel_mode_without_cuda_raises():
+    from deepshift_b200 import kernels, modules
+    lin = modules.LinearShift(4, 2, use_kernel=True, use_cuda=False)
+    with pytest.raises(RuntimeError, match="no CPU kernel path"):
+        lin(torch.zeros(1, 4))
+    with pytest.raises(RuntimeError, match="no CPU kernel path"):
+        kernels.linear(torch.zeros(1, 4, dtype=torch.int32), torch.zeros(2, 4), None, use_cuda=False)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        from deepshift_b200.utils import ConcWeight
+        kernels.linear(torch.zeros(1, 4, dtype=torch.int32), torch.zeros(2, 4), None, None,
+                       ConcWeight(torch.zeros(2, dtype=torch.int32), 0, 3))
+
+
+# --------------------------------------------------------------------------- workloads
+def test_workload_shift_op_counts():
+    from deepshift_b200 import workloads as W
+    assert W.mnist_fc().shift_ops() == 668672
+    assert W.mnist_conv().shift_ops() == 2293000
+    assert W.resnet20().shift_ops() == 40551040
+    r18 = W.resnet18()
+    assert r18.shift_ops() == 1814073344
+    assert sum(1 for l in r18.layers if l.kind == 'conv') == 20 and sum(1 for l in r18.layers if l.kind == 'linear') == 1
+
+
+def test_workload_generators_are_seeded_and_in_range():
+    from deepshift_b200 import workloads as W
+    net = W.mnist_conv()
+    a, b = W.make_weights(net), W.make_weights(net)
+    for wa, wb in zip(a, b):
+        assert torch.equal(wa['shift'], wb['shift']) and torch.equal(wa['sign'], wb['sign'])
+        assert int(wa['shift'].min()) >= -15 and int(wa['shift'].max()) <= 0
+        assert set(wa['sign'].unique().tolist()) <= {-1, 0, 1}
+        assert torch.equal(wa['bias'], torch.floor(wa['bias'] * 4096) / 4096)
+    frac0 = float((a[2]['sign'] == 0).float().mean())
+    assert 0.08 < frac0 < 0.12
+    x0, x1 = W.make_input(net, 4, rank=0), W.make_input(net, 4, rank=1)
+    assert x0.shape == (4, 1, 28, 28) and not torch.equal(x0, x1)
+    assert float(x0.min()) >= -8.0 and float(x0.max()) <= 7.0
+
+
+def test_oracle_network_runs_on_cpu(oracle):
+    """The oracle executor alone (no GPU): shapes and determinism of a small ResNet-20 pass."""
+    from deepshift_b200 import workloads as W
+    from helpers import np_weights
+    from oracle import reference_nets as R
+    net = W.resnet20()
+    ws = np_weights(W.make_weights(net))
+    x = W.make_input(net, 2).numpy()
+    y = R.forward(net, ws, x)
+    assert y.shape == (2, 10) and y.dtype == np.float32
+    assert np.array_equal(y, R.forward(net, ws, x))
+    assert np.array_equal(y[:1], R.forward(net, ws, x[:1]))
+
+
+# --------------------------------------------------------------------------- C ABI
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "deepshift_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ds_[a-z0-9_]+)\s*\(", text)))
+
+
+def _library():
+    from deepshift_b200 import _build
+    if not os.path.exists(_build.LIB_PATH):
+        if _build.nvcc_path() is None:
+            pytest.skip("CUDA library not built and no nvcc here")
+        _build.build()
+    return ctypes.CDLL(_build.LIB_PATH)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _library()
+    names = _declared_functions()
+    assert {"ds_linear_i32", "ds_conv2d_i32", "ds_compress", "ds_linear_ex", "ds_conv2d_ex", "ds_strerror"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_argument_checks_need_no_gpu():
+    """Bad arguments are rejected before any CUDA call."""
+    from deepshift_b200 import _ffi
+    lib = _ffi.lib()
+    assert lib.ds_linear_i32(None, None, None, None, 4, 4, 4, 3, 0, 0, None) == 1
+    assert lib.ds_linear_i32(None, None, None, None, 4, 0, 4, 3, 0, 0, None) == 1
+    assert lib.ds_linear_i32(None, None, None, None, 0, 4, 4, 3, 0, 0, None) == 0  # empty batch
+    assert lib.ds_conv2d_i32(None, None, None, None, 1, 1, 4, 4, 1, 5, 5, 1, 1, 0, 0, 3, 0, 0, None) == 1
+    assert lib.ds_compress(None, None, None, 1, 1, 3, 0, None) == 1
+    assert lib.ds_compress(16, 16, 16, 1, 1, 9, 0, None) == 2
+    assert b"unsupported" in lib.ds_strerror(2)
+    assert lib.ds_version() >= 100
+    with pytest.raises(RuntimeError, match="bad argument"):
+        _ffi.check(1, "probe")
