@@ -28,11 +28,12 @@ constexpr int WS_BM = 256;     // rows of x per CTA
 constexpr int WS_BKT = 28;     // largest k-tile
 constexpr int WS_STAGES = 2;
 // Register split after the roles part.  The CTA starts with 768 * 80 registers; what the
-// producers give back (256 * (80 - 48) = 8192) is all the consumers can take (512 * (96 - 80) =
-// 8192): a larger request would wait for registers that never come.
-constexpr int WS_LAUNCH_REGS = 80, WS_PROD_REGS = 48, WS_CONS_REGS = 96;
+// producers give back (256 * (80 - 56) = 6144) is all the consumers can take (512 * (88 - 80) =
+// 4096): a larger request would wait for registers that never come.
+constexpr int WS_LAUNCH_REGS = 80, WS_PROD_REGS = 56, WS_CONS_REGS = 88;
 static_assert(WS_CONS * (WS_CONS_REGS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - WS_PROD_REGS), "register pool");
-constexpr int WS_WAIT_LIMIT = 1 << 20;  // polls of one mbarrier wait before giving up
+constexpr int WS_WAIT_LIMIT = 1 << 12;  // rounds of one mbarrier wait before giving up
+constexpr unsigned WS_WAIT_NS = 1000000;  // suspend-time hint of one round, nanoseconds
 
 __device__ int g_ws_error = 0;  // set when a bounded wait ran out (never in a correct run)
 
@@ -63,19 +64,21 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Bounded wait for the phase with the given parity to complete.  Returns false on give-up.
+// Bounded wait for the phase with the given parity to complete.  Each try_wait lets the hardware
+// suspend the thread for up to WS_WAIT_NS before it reports "not yet", so a waiting warp issues
+// almost nothing.  Returns false after WS_WAIT_LIMIT such rounds (seconds; a correct run waits
+// microseconds).
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity)
 {
     const unsigned addr = smem_u32(bar);
     for (int i = 0; i < WS_WAIT_LIMIT; ++i) {
         unsigned ok;
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(WS_WAIT_NS)
             : "memory");
         if (ok) return true;
-        __nanosleep(32);  // leave the issue slots to the warps that make progress
     }
     return false;
 }
@@ -152,106 +155,48 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         const int32_t* wrow = (n0 + wn < p.N) ? p.packed + (long long)(n0 + wn) * p.dec.row_len : nullptr;
         const uint32_t fmask = (1u << p.dec.fw) - 1u;
 
-        // Gathers and stores the x tile of one k-tile.  INK: input kind; LAST: the tile may
-        // reach past K, where x is stored as 0 (see the weight tail below).
-        auto stage_x = [&](auto ink_tag, auto last_tag, int st, int k0) {
-            constexpr int INK = decltype(ink_tag)::value;
-            constexpr bool LAST = decltype(last_tag)::value;
-            const int padv = (INK != INK_F32) ? 0 : kPadMarker;
+        // Registers that hold one k-tile of this thread's x values and weight words between the
+        // global loads (issued one tile ahead) and their conversion into shared memory.
+        constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows of the largest k-tile, row mode
+        constexpr int XN = ROW ? RMAX * KW : WS_BKT;      // x values per thread per tile (conv)
+        constexpr int LIN_RP = WS_PROD / 32;              // linear: x rows per pass
+        constexpr int LIN_N = BM / LIN_RP;                // linear: x values per thread per tile
+        constexpr int XREG = CONV ? XN * PIX : LIN_N;
+        int xr[XREG];
+        uint32_t w_reg[EW];
+        static_assert(XREG <= 32, "producer registers");
+
+        auto fill_table = [&](int tile) {
+            if (!CONV || pt >= WS_BKT) return;
+            KEntry e;
+            e.pad = 0;
+            e.off = 0;
+            e.kh = 31;
+            e.kw = 0;
             if (ROW) {
-                // UR rows of the k-tile at a time: 2 * UR * KW loads in flight per thread
-                constexpr int UR = (KW == 1) ? 4 : (KW == 3 ? 4 : 2);
-                for (int r0 = 0; r0 < p.rows_per_tile; r0 += UR) {
-                    int v[PIX][UR][KW];
-#pragma unroll
-                    for (int u = 0; u < UR; ++u) {
-                        const int2 e = *reinterpret_cast<const int2*>(&s.ktab[st][r0 + u]);
-#pragma unroll
-                        for (int q = 0; q < PIX; ++q) {
-                            const bool rv = (rowmask[q] >> e.y) & 1u;
-                            const int* rowp = reinterpret_cast<const int*>(x_pix[q] + e.x);
-#pragma unroll
-                            for (int kw = 0; kw < KW; ++kw) {
-                                int val = padv;
-                                if (rv && (colmask[q] & (1u << kw))) val = __ldg(rowp + kw);
-                                v[q][u][kw] = val;
-                            }
-                        }
-                    }
-                    float* dst = &s.a[st][r0 * KW][pt];
-#pragma unroll
-                    for (int u = 0; u < UR; ++u)
-#pragma unroll
-                        for (int q = 0; q < PIX; ++q)
-#pragma unroll
-                            for (int kw = 0; kw < KW; ++kw) {
-                                float o = operand_of<true, INK>(p, v[q][u][kw]);
-                                if (LAST && k0 + (r0 + u) * KW + kw >= p.K) o = 0.f;
-                                dst[(u * KW + kw) * S::AP + q * WS_PROD] = o;
-                            }
-                }
-            } else if (CONV) {
-                constexpr int UK = 4;  // columns of the k-tile at a time
-                for (int kb = 0; kb < p.bk; kb += UK) {
-                    int v[PIX][UK];
-#pragma unroll
-                    for (int u = 0; u < UK; ++u) {
-                        const int4 e = *reinterpret_cast<const int4*>(&s.ktab[st][kb + u]);
-#pragma unroll
-                        for (int q = 0; q < PIX; ++q) {
-                            int val = padv;
-                            if (((rowmask[q] >> e.y) & (colmask[q] >> e.z) & 1u) != 0u)
-                                val = __ldg(reinterpret_cast<const int*>(x_pix[q] + e.x));
-                            v[q][u] = val;
-                        }
-                    }
-                    float* dst = &s.a[st][kb][pt];
-#pragma unroll
-                    for (int u = 0; u < UK; ++u)
-#pragma unroll
-                        for (int q = 0; q < PIX; ++q) {
-                            float o = operand_of<true, INK>(p, v[q][u]);
-                            if (LAST && k0 + kb + u >= p.K) o = 0.f;
-                            dst[u * S::AP + q * WS_PROD] = o;
-                        }
+                const int row = tile * p.rows_per_tile + pt;  // global (ic,kh) row index
+                if (pt < p.rows_per_tile && row < p.C * p.KH) {
+                    const int ic = magic_div(row, p.magic_kh);
+                    e.kh = row - ic * p.KH;
+                    e.off = (ic * p.H * p.W + e.kh * p.W) * 4;
                 }
             } else {
-                // x is [M,K]: lanes run along k (32 wide), RP rows per pass, UP passes at a time
-                constexpr int RP = WS_PROD / 32;
-                const int kl = pt & 31;
-                const bool kval = kl < p.bk && k0 + kl < p.K;
-                constexpr int UP = 8;
-                for (int mb = 0; mb < BM; mb += RP * UP) {
-                    int v[UP];
-#pragma unroll
-                    for (int u = 0; u < UP; ++u) {
-                        const int ml = mb + RP * u + (pt >> 5);
-                        int val = padv;
-                        if (kval && m0 + ml < p.M)
-                            val = __ldg(static_cast<const int32_t*>(p.x) + ((long long)(m0 + ml) * p.K + k0 + kl));
-                        v[u] = val;
-                    }
-                    if (kl < WS_BKT) {
-#pragma unroll
-                        for (int u = 0; u < UP; ++u) {
-                            const int ml = mb + RP * u + (pt >> 5);
-                            float o = operand_of<true, INK>(p, v[u]);
-                            if (LAST && k0 + kl >= p.K) o = 0.f;
-                            s.a[st][kl][ml] = o;
-                        }
-                    }
+                const int k = tile * p.bk + pt;
+                if (pt < p.bk && k < p.K) {
+                    const int ic = magic_div(k, p.magic_khw);
+                    const int tap = k - ic * (p.KH * p.KW);
+                    e.kh = magic_div(tap, p.magic_kw);
+                    e.kw = tap - e.kh * p.KW;
+                    e.off = (ic * p.H * p.W + e.kh * p.W + e.kw) * 4;
                 }
             }
+            s.ktab[tile & 1][pt] = e;
         };
 
-        for (int tile = 0; tile < p.ntiles; ++tile) {
-            const int st = tile & 1;
-            if (tile >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned((tile >> 1) - 1) & 1u)) s.err = 1;
-            const int k0 = tile * p.bk;
-            const bool last = tile + 1 >= p.ntiles;
-
-            // weight words of this tile (issued first: their latency hides behind the x gather)
-            uint32_t w_reg[EW];
+        // Issues the global loads of one k-tile into registers.  Positions outside the image or
+        // the matrix get `padv` (0, or the marker that stands for an unquantised 0 for fp32 kinds).
+        auto issue_loads = [&](int tile) {
+            const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
             const int w0 = tile * p.kt_words;
 #pragma unroll
             for (int e = 0; e < EW; ++e) {
@@ -260,73 +205,148 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len) w = uint32_t(__ldg(wrow + w0 + jw));
                 w_reg[e] = w;
             }
-
-            // per-tile table of k -> (offset, kh[, kw])
-            if (CONV && pt < WS_BKT) {
-                KEntry e;
-                e.pad = 0;
-                e.off = 0;
-                e.kh = 31;
-                e.kw = 0;
-                if (ROW) {
-                    const int row = tile * p.rows_per_tile + pt;  // global (ic,kh) row index
-                    if (pt < p.rows_per_tile && row < p.C * p.KH) {
-                        const int ic = magic_div(row, p.magic_kh);
-                        e.kh = row - ic * p.KH;
-                        e.off = (ic * p.H * p.W + e.kh * p.W) * 4;
-                    }
-                } else {
-                    const int k = k0 + pt;
-                    if (pt < p.bk && k < p.K) {
-                        const int ic = magic_div(k, p.magic_khw);
-                        const int tap = k - ic * (p.KH * p.KW);
-                        e.kh = magic_div(tap, p.magic_kw);
-                        e.kw = tap - e.kh * p.KW;
-                        e.off = (ic * p.H * p.W + e.kh * p.W + e.kw) * 4;
-                    }
-                }
-                s.ktab[st][pt] = e;
-            }
-            if (CONV) producer_bar();
-
-            with_input_kind(p, [&](auto ink_tag) {
-                if (last) stage_x(ink_tag, std::true_type(), st, k0);
-                else stage_x(ink_tag, std::false_type(), st, k0);
-            });
-
-            // ---- weight tile: decode through the table ------------------------------------------------
-            // Slots k >= K of the last words decode like any field (a zero field is -2^0); the x
-            // values stored above are 0 there, so they add nothing, and the epilogue takes their
-            // share (tail_neg) out of the negative-weight count.
-            int negs = 0;
-            auto decode = [&](auto num_tag) {
-                constexpr int NUM = decltype(num_tag)::value;
+            const int tb = tile & 1;
+            if (ROW) {
 #pragma unroll
-                for (int e = 0; e < EW; ++e) {
-                    const int jw = (pt + e * WS_PROD) / BN;
-                    if (jw < p.kt_words) {
-                        uint32_t w = w_reg[e];
-                        float* dst = &s.b[st][jw * NUM][wn];
+                for (int u = 0; u < RMAX; ++u) {
+                    const int2 e = *reinterpret_cast<const int2*>(&s.ktab[tb][u]);  // rows past the tile: kh = 31
 #pragma unroll
-                        for (int i = 0; i < NUM; ++i) {
-                            const int v0 = s.lut0[w & fmask];
-                            w >>= p.dec.fw;
-                            dst[i * BN] = __int_as_float(v0);
-                            negs += int(uint32_t(v0) >> 31);
+                    for (int q = 0; q < PIX; ++q) {
+                        const bool rv = (rowmask[q] >> e.y) & 1u;
+                        const int* rowp = reinterpret_cast<const int*>(x_pix[q] + e.x);
+#pragma unroll
+                        for (int kw = 0; kw < KW; ++kw) {
+                            int val = padv;
+                            if (rv && (colmask[q] & (1u << kw))) val = __ldg(rowp + kw);
+                            xr[(q * RMAX + u) * KW + kw] = val;
                         }
                     }
                 }
-            };
-            switch (p.dec.num) {
-                case 4: decode(std::integral_constant<int, 4>()); break;
-                case 5: decode(std::integral_constant<int, 5>()); break;
-                case 6: decode(std::integral_constant<int, 6>()); break;
-                case 8: decode(std::integral_constant<int, 8>()); break;
-                case 10: decode(std::integral_constant<int, 10>()); break;
-                default: decode(std::integral_constant<int, 16>()); break;
+            } else if (CONV) {
+#pragma unroll
+                for (int u = 0; u < WS_BKT; ++u) {
+                    const int4 e = *reinterpret_cast<const int4*>(&s.ktab[tb][u]);
+#pragma unroll
+                    for (int q = 0; q < PIX; ++q) {
+                        int val = padv;
+                        if (((rowmask[q] >> e.y) & (colmask[q] >> e.z) & 1u) != 0u)
+                            val = __ldg(reinterpret_cast<const int*>(x_pix[q] + e.x));
+                        xr[q * WS_BKT + u] = val;
+                    }
+                }
+            } else {
+                // x is [M,K]: lanes run along k (32 wide), LIN_RP rows per pass
+                const int kl = pt & 31;
+                const int k = tile * p.bk + kl;
+                const bool kval = kl < p.bk && k < p.K;
+#pragma unroll
+                for (int u = 0; u < LIN_N; ++u) {
+                    const int ml = LIN_RP * u + (pt >> 5);
+                    int val = padv;
+                    if (kval && m0 + ml < p.M)
+                        val = __ldg(static_cast<const int32_t*>(p.x) + ((long long)(m0 + ml) * p.K + k));
+                    xr[u] = val;
+                }
+            }
+        };
+
+        // Converts the registers of one k-tile and stores them into stage `st`.  INK: input kind;
+        // LAST: the tile may reach past K, where x is stored as 0 (see the weight tail below).
+        auto store_x = [&](auto ink_tag, auto last_tag, int st, int k0) {
+            constexpr int INK = decltype(ink_tag)::value;
+            constexpr bool LAST = decltype(last_tag)::value;
+            if (ROW) {
+#pragma unroll
+                for (int u = 0; u < RMAX; ++u) {
+                    if (u < p.rows_per_tile) {
+#pragma unroll
+                        for (int q = 0; q < PIX; ++q)
+#pragma unroll
+                            for (int kw = 0; kw < KW; ++kw) {
+                                float o = operand_of<true, INK>(p, xr[(q * RMAX + u) * KW + kw]);
+                                if (LAST && k0 + u * KW + kw >= p.K) o = 0.f;
+                                s.a[st][u * KW + kw][pt + q * WS_PROD] = o;
+                            }
+                    }
+                }
+            } else if (CONV) {
+#pragma unroll
+                for (int u = 0; u < WS_BKT; ++u) {
+                    if (u < p.bk) {
+#pragma unroll
+                        for (int q = 0; q < PIX; ++q) {
+                            float o = operand_of<true, INK>(p, xr[q * WS_BKT + u]);
+                            if (LAST && k0 + u >= p.K) o = 0.f;
+                            s.a[st][u][pt + q * WS_PROD] = o;
+                        }
+                    }
+                }
+            } else {
+                const int kl = pt & 31;
+                if (kl < WS_BKT) {
+#pragma unroll
+                    for (int u = 0; u < LIN_N; ++u) {
+                        float o = operand_of<true, INK>(p, xr[u]);
+                        if (LAST && k0 + kl >= p.K) o = 0.f;
+                        s.a[st][kl][LIN_RP * u + (pt >> 5)] = o;
+                    }
+                }
+            }
+        };
+
+        // Decodes this thread's weight words through the table into stage `st`.  Slots k >= K of
+        // the last words decode like any field (a zero field is -2^0); the x values stored there
+        // are 0, so they add nothing, and the epilogue takes their share (tail_neg) out of the
+        // negative-weight count.
+        auto store_w = [&](auto num_tag, int st) {
+            constexpr int NUM = decltype(num_tag)::value;
+            int negs = 0;
+#pragma unroll
+            for (int e = 0; e < EW; ++e) {
+                const int jw = (pt + e * WS_PROD) / BN;
+                if (jw < p.kt_words) {
+                    uint32_t w = w_reg[e];
+                    float* dst = &s.b[st][jw * NUM][wn];
+#pragma unroll
+                    for (int i = 0; i < NUM; ++i) {
+                        const int v0 = s.lut0[w & fmask];
+                        w >>= p.dec.fw;
+                        dst[i * BN] = __int_as_float(v0);
+                        negs += int(uint32_t(v0) >> 31);
+                    }
+                }
             }
             if (negs) atomicAdd(&s.negc[wn], negs);
+        };
+
+        // Loads run one k-tile ahead of the stores: while this thread waits for a free stage, the
+        // loads of the tile it will store next are already in flight.
+        fill_table(0);
+        if (CONV) producer_bar();
+        issue_loads(0);
+        for (int tile = 0; tile < p.ntiles; ++tile) {
+            const int st = tile & 1;
+            if (tile >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned((tile >> 1) - 1) & 1u)) s.err = 1;
+            const int k0 = tile * p.bk;
+            const bool last = tile + 1 >= p.ntiles;
+            with_input_kind(p, [&](auto ink_tag) {
+                if (last) store_x(ink_tag, std::true_type(), st, k0);
+                else store_x(ink_tag, std::false_type(), st, k0);
+            });
+            switch (p.dec.num) {
+                case 4: store_w(std::integral_constant<int, 4>(), st); break;
+                case 5: store_w(std::integral_constant<int, 5>(), st); break;
+                case 6: store_w(std::integral_constant<int, 6>(), st); break;
+                case 8: store_w(std::integral_constant<int, 8>(), st); break;
+                case 10: store_w(std::integral_constant<int, 10>(), st); break;
+                default: store_w(std::integral_constant<int, 16>(), st); break;
+            }
             mbar_arrive(&s.full[st]);
+            if (!last) {
+                fill_table(tile + 1);
+                if (CONV) producer_bar();
+                issue_loads(tile + 1);
+            }
         }
         if (s.err) g_ws_error = 1;
         return;
