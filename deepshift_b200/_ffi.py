@@ -21,6 +21,7 @@ class Fuse(ctypes.Structure):
         ("relu", ctypes.c_int), ("requant", ctypes.c_int),
         ("residual", ctypes.c_void_p), ("act_bits", ctypes.c_int),
         ("round_f32", ctypes.c_int), ("reserved", ctypes.c_int * 3),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_longlong),
     ]
 
 

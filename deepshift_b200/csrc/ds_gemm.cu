@@ -400,7 +400,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     // ---- epilogue -----------------------------------------------------------------------------
     store_tile<TN, CONV>(
         p, m0, n0, tm, tn, BM, BN,
-        [&](int i, int j) -> int {
+        [&](int i, int j, long long) -> int {
             if (FP) return s.accs[(i * TN + j) * NT + t] - ndrains * kMagicBits;
             return acc[FP ? 0 : i][FP ? 0 : j];
         },
@@ -513,6 +513,10 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.relu = f.relu;
     p.requant = f.requant;
     p.round_f32 = f.round_f32;
+    p.splits = 1;
+    p.counters = static_cast<int*>(f.workspace);
+    p.counter_slots = f.workspace ? f.workspace_bytes / 4 : 0;
+    if (f.workspace && ((reinterpret_cast<uintptr_t>(f.workspace) & 3u) || f.workspace_bytes < 0)) return DS_ERR_BAD_ARG;
     p.residual = f.residual;
     p.q.scale = float(1ll << (needs_if ? F : 0));
     p.inv_scale = 1.0f / p.q.scale;

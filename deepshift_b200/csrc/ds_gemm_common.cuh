@@ -31,6 +31,11 @@ struct GemmParams {
     int rows_per_tile;  // row mode: (ic,kh) rows per k-tile = bk / KW
     // fused prologue / epilogue
     int in_kind, out_kind, relu, requant, round_f32;
+    // split-K (warp-specialised kernel): gridDim.z CTAs share one output tile
+    int splits;          // 1 = off
+    int tiles_per_split; // k-tiles per split
+    int* counters;       // one arrival counter per output tile, zero between launches
+    long long counter_slots;
     Quant q;
     int rq_lo, rq_hi;
     float inv_scale;  // 2^-F
@@ -55,8 +60,8 @@ __device__ __forceinline__ int magic_div(int k, unsigned magic) { return magic ?
 // Epilogue shared by both kernels: v = acc + bias (+ negative-weight count), optional residual
 // add, ReLU, requantise clamp, then int32 or fp32 store.  Thread (tm, tn) owns rows
 // 4*tm..4*tm+3 and BM/2 + the same, and columns 4*tn..4*tn+3 (and BN/2 + the same when TN == 8)
-// of the CTA tile at (m0, n0).  `accv(i, j)` returns the finished integer sum, `colc(j)` the
-// per-column constant added to it.
+// of the CTA tile at (m0, n0).  `accv(i, j, o)` returns the finished integer sum of the element
+// whose offset in the output is o, `colc(col)` the per-column constant added to it.
 template <int TN, bool CONV, class AccFn, class ColFn>
 __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, int tm, int tn, int BM, int BN,
                                            AccFn accv, ColFn colc)
@@ -103,7 +108,7 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                     const long long o = ((long long)b * p.OC + n) * p.P + pp;
                     int v[4];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j) + addc[j], o + i);
+                    for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j, o + i) + addc[j], o + i);
                     if (p.out_kind == DS_OUT_I32) {
                         *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
                     } else {
@@ -123,7 +128,7 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                         const int n = n0 + ncol(j);
                         if (n >= p.N) continue;
                         const long long o = ((long long)b * p.OC + n) * p.P + pp;
-                        const int v = finish(accv(4 * h + i, j) + addc[j], o);
+                        const int v = finish(accv(4 * h + i, j, o) + addc[j], o);
                         if (p.out_kind == DS_OUT_I32) oi[o] = v;
                         else of[o] = __int2float_rn(v) * p.inv_scale;
                     }
@@ -143,7 +148,7 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                 if (vec && n + 3 < p.N) {
                     int v[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
+                    for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j, o + j) + addc[4 * h + j], o + j);
                     if (p.out_kind == DS_OUT_I32) {
                         *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
                     } else {
@@ -155,12 +160,44 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (n + j >= p.N) continue;
-                        const int v = finish(accv(i, 4 * h + j) + addc[4 * h + j], o + j);
+                        const int v = finish(accv(i, 4 * h + j, o + j) + addc[4 * h + j], o + j);
                         if (p.out_kind == DS_OUT_I32) oi[o + j] = v;
                         else of[o + j] = __int2float_rn(v) * p.inv_scale;
                     }
                 }
             }
+        }
+    }
+}
+
+// Split-K: adds this CTA's partial sums (plus `colc`, without bias or epilogue) into the output
+// slots, which the host zeroed before the launch.  Integer adds commute, so the result does not
+// depend on the order in which the splits arrive.  Same element mapping as store_tile.
+template <int TN, bool CONV, class AccFn, class ColFn>
+__device__ __forceinline__ void reduce_tile(const GemmParams& p, int m0, int n0, int tm, int tn, int BM, int BN,
+                                            AccFn accv, ColFn colc)
+{
+    auto ncol = [&](int j) { return (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j); };
+    auto mrow = [&](int i) { return (i >= 4) ? (BM / 2 + 4 * tm + i - 4) : (4 * tm + i); };
+    int* oi = static_cast<int*>(p.out);
+#pragma unroll
+    for (int i = 0; i < kTM; ++i) {
+        const int m = m0 + mrow(i);
+        if (m >= p.M) continue;
+        long long rowoff, nstride;
+        if (CONV) {
+            const int b = m / p.P, pp = m - b * p.P;
+            rowoff = (long long)b * p.OC * p.P + pp;
+            nstride = p.P;
+        } else {
+            rowoff = (long long)m * p.N;
+            nstride = 1;
+        }
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + ncol(j);
+            if (n >= p.N) continue;
+            atomicAdd(oi + rowoff + n * nstride, accv(i, j, 0) + colc(ncol(j)));
         }
     }
 }

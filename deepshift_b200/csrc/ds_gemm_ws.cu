@@ -49,6 +49,7 @@ struct WsSmem {
     int lut0[256];  // float bits of the decoded weight per field value
     int negc[BN];   // negative weights per output column
     int err;
+    int last_flag;  // split-K: this CTA arrived last at its tile's counter
     int accs[kTM * TN * WS_CONS];  // drained accumulators, [slot][consumer thread]
 };
 
@@ -83,6 +84,8 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     return false;
 }
 
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 2, %0;" ::"n"(WS_CONS) : "memory"); }
+
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(WS_PROD) : "memory"); }
 
 // ---------------------------------------------------------------------------------------------
@@ -103,6 +106,10 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     const int t = threadIdx.x;
     const int m0 = blockIdx.x * BM;
     const int n0 = blockIdx.y * BN;
+    // split-K: this CTA handles k-tiles [t_begin, t_end)
+    const int t_begin = blockIdx.z * p.tiles_per_split;
+    const int t_end = min(p.ntiles, t_begin + p.tiles_per_split);
+    const int my_tiles = t_end - t_begin;
 
     // ---- set-up by all 640 threads ----------------------------------------------------------------
     for (int f = t; f < (1 << p.dec.fw); f += WS_NT) {
@@ -321,12 +328,13 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 
         // Loads run one k-tile ahead of the stores: while this thread waits for a free stage, the
         // loads of the tile it will store next are already in flight.
-        fill_table(0);
+        fill_table(t_begin);
         if (CONV) producer_bar();
-        issue_loads(0);
-        for (int tile = 0; tile < p.ntiles; ++tile) {
-            const int st = tile & 1;
-            if (tile >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned((tile >> 1) - 1) & 1u)) s.err = 1;
+        issue_loads(t_begin);
+        for (int it = 0; it < my_tiles; ++it) {
+            const int tile = t_begin + it;
+            const int st = it & 1;
+            if (it >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned((it >> 1) - 1) & 1u)) s.err = 1;
             const int k0 = tile * p.bk;
             const bool last = tile + 1 >= p.ntiles;
             with_input_kind(p, [&](auto ink_tag) {
@@ -342,7 +350,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 default: store_w(std::integral_constant<int, 16>(), st); break;
             }
             mbar_arrive(&s.full[st]);
-            if (!last) {
+            if (it + 1 < my_tiles) {
                 fill_table(tile + 1);
                 if (CONV) producer_bar();
                 issue_loads(tile + 1);
@@ -374,9 +382,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 
     int ndrains = 0, since = 0;
     bool bad = false;
-    for (int tile = 0; tile < p.ntiles; ++tile) {
-        const int st = tile & 1;
-        if (!mbar_wait(&s.full[st], unsigned(tile >> 1) & 1u)) bad = true;
+    for (int it = 0; it < my_tiles; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&s.full[st], unsigned(it >> 1) & 1u)) bad = true;
 #pragma unroll 4
         for (int k = 0; k < p.bk; ++k) {
             float a[kTM], b[TN];
@@ -391,7 +399,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
         }
         mbar_arrive(&s.empty[st]);
-        if (++since == p.flush_tiles || tile + 1 == p.ntiles) {
+        if (++since == p.flush_tiles || it + 1 == my_tiles) {
             // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
             // slots and restart them; the epilogue removes ndrains * kMagicBits.
 #pragma unroll
@@ -407,10 +415,37 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     }
     if (bad) g_ws_error = 1;
 
-    store_tile<TN, CONV>(
+    // tail_neg belongs to the split that holds the last k-tile
+    const int tailc = (t_end == p.ntiles) ? p.tail_neg : 0;
+    if (p.splits == 1) {
+        store_tile<TN, CONV>(
+            p, m0, n0, tm, tn, BM, BN,
+            [&](int i, int j, long long) -> int { return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits; },
+            [&](int col) -> int { return s.negc[col] - tailc; });
+        return;
+    }
+    // ---- split-K: add the partial sums into the zeroed output, then the CTA that arrives last at
+    // this tile's counter reads the totals back and applies the epilogue in place.
+    reduce_tile<TN, CONV>(
         p, m0, n0, tm, tn, BM, BN,
-        [&](int i, int j) -> int { return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits; },
-        [&](int col) -> int { return s.negc[col] - p.tail_neg; });
+        [&](int i, int j, long long) -> int { return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits; },
+        [&](int col) -> int { return s.negc[col] - tailc; });
+    __threadfence();
+    consumer_bar();
+    if (t == 0) {
+        int* cnt = p.counters + (blockIdx.y * gridDim.x + blockIdx.x);
+        const int prev = atomicAdd(cnt, 1);
+        const int lastone = (prev == p.splits - 1);
+        if (lastone) *cnt = 0;  // ready for the next launch
+        s.last_flag = lastone;
+    }
+    consumer_bar();
+    if (!s.last_flag) return;
+    __threadfence();
+    const int* tot = static_cast<const int*>(p.out);
+    store_tile<TN, CONV>(
+        p, m0, n0, tm, tn, BM, BN, [&](int, int, long long o) -> int { return __ldcg(tot + o); },
+        [&](int) -> int { return 0; });
 }
 
 // Chooses the k-tile: a multiple of num (whole packed words) and of the staging granularity
@@ -457,7 +492,39 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     if (attr_state < 0) return DS_ERR_UNSUPPORTED;
     const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
     if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
-    kern<<<dim3((unsigned)gx, (unsigned)gy), WS_NT, smem, st>>>(p);
+    // Split-K when the output tiles alone fill the SMs badly (few tiles, or a last wave that is
+    // mostly empty) and the caller gave a counter workspace: gridDim.z CTAs share a tile.
+    p.splits = 1;
+    p.tiles_per_split = p.ntiles;
+    const long long tiles = gx * gy;
+    if (p.counters && tiles <= p.counter_slots && p.ntiles >= 16) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+                sms = 148;
+        }
+        auto eff = [&](int sp) {
+            const long long ctas = tiles * sp, waves = (ctas + sms - 1) / sms;
+            return double(ctas) / double(waves * sms);
+        };
+        double best = eff(1);
+        for (int sp = 2; sp <= 4; ++sp) {
+            if (p.ntiles / sp < 8) break;
+            const double e = eff(sp) * 0.92;  // measured cost of zeroing, atomics and the second pass
+            if (e > best * 1.05) {
+                best = e;
+                p.splits = sp;
+            }
+        }
+        if (p.splits > 1) {
+            p.tiles_per_split = (p.ntiles + p.splits - 1) / p.splits;
+            p.splits = (p.ntiles + p.tiles_per_split - 1) / p.tiles_per_split;
+            if (cudaMemsetAsync(p.out, 0, size_t(p.M) * size_t(p.N) * 4, st) != cudaSuccess) return DS_ERR_CUDA;
+        }
+    }
+    kern<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)p.splits), WS_NT, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

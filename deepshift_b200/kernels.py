@@ -45,8 +45,23 @@ def _no_cpu():
     raise RuntimeError("deepshift_b200 has no CPU kernel path: use_cuda must be True")
 
 
+_WORKSPACES = {}
+
+
+def workspace(device):
+    """Per-device zeroed scratch for split-K arrival counters (see ds_fuse_t.workspace); kernels
+    leave it zero, so one tensor serves every launch on the device's streams in order."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    ws = _WORKSPACES.get(device)
+    if ws is None:
+        ws = _WORKSPACES[device] = torch.zeros(16384, dtype=torch.int32, device=device)
+    return ws
+
+
 def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=False, requant=False,
-          residual=None, act_bits=0, round_f32=False):
+          residual=None, act_bits=0, round_f32=False, workspace=None):
     f = _ffi.Fuse()
     f.in_kind, f.out_kind = in_kind, out_kind
     f.act_integer_bits, f.act_fraction_bits = int(act_integer_bits), int(act_fraction_bits)
@@ -54,6 +69,9 @@ def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=F
     f.residual = residual.data_ptr() if residual is not None else None
     f.act_bits = int(act_bits)
     f.round_f32 = int(bool(round_f32))
+    if workspace is not None:
+        f.workspace = workspace.data_ptr()
+        f.workspace_bytes = workspace.numel() * workspace.element_size()
     return f
 
 
@@ -166,7 +184,8 @@ def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0
         _check_tensor(residual, "residual", torch.int32)
         if residual.shape != out.shape:
             raise RuntimeError("residual shape %s != output shape %s" % (tuple(residual.shape), tuple(out.shape)))
-    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32)
+    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32,
+              workspace(input.device))
     with torch.cuda.device(input.device):
         rc = _ffi.lib().ds_conv2d_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),

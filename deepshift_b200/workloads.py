@@ -304,7 +304,7 @@ class IntPipeline:
                 res = t[o['add']] if o.get('add') else None
                 fuse = kernels._fuse(in_kind, _ffi.OUT_F32 if lastlayer else _ffi.OUT_I32, self.I, self.F,
                                      relu=bool(o.get('relu')), requant=False, residual=res,
-                                     round_f32=not lastlayer)
+                                     round_f32=not lastlayer, workspace=kernels.workspace(dev))
                 self.calls.append((op, xin, li, L, out, fuse, res))
                 dst = o.get('dst', 'x')
                 t[dst], fp32[dst] = out, lastlayer

@@ -80,6 +80,13 @@ typedef struct {
                                to sums beyond 2^24, so that an int32 tensor handed to the next layer
                                holds exactly the value the reference's fp32 tensor would        */
     int reserved[3];
+    void *workspace;        /* optional scratch for split-K: int32 arrival counters, one per output
+                               tile (256 rows x 128 or 64 columns).  Zero it once; every launch leaves
+                               it zero.  With it, layers whose tiles fill the SMs badly are split
+                               along K (the output is zeroed, partial sums are added with integer
+                               atomics, the last CTA of a tile applies the epilogue).  NULL = never
+                               split.  Launches that share a workspace must not overlap on the GPU. */
+    long long workspace_bytes;
 } ds_fuse_t;
 
 /*

@@ -302,3 +302,29 @@ def test_no_kernel_wait_ran_out(cuda_device):
     flag = ctypes.c_int(-1)
     assert _ffi.lib().ds_last_kernel_error(ctypes.byref(flag)) == 0
     assert flag.value == 0
+
+
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_conv_split_k_with_workspace(oracle, cuda_device, out_f32):
+    """Few output tiles and a long K: the launch is split along K (integer atomics into the zeroed
+    output, the last CTA of a tile applies the epilogue).  Same bits as the unsplit result, twice
+    in a row (the arrival counters return to zero)."""
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(21)
+    B, C, H, OC = 5, 128, 7, 130
+    I, F = 4, 12
+    x = acts_q16(rng, (B, C, H, H))
+    shift, sign = weights(rng, (OC, C, 3, 3))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    res = rng.integers(-50000, 50000, (B, OC, H, H)).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    ref = oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1))
+    ref = np.maximum(ref.astype(np.float32) + res.astype(np.float32), 0).astype(np.int64).astype(np.int32)
+    want = oracle.from_fixed(ref, F) if out_f32 else ref
+    for _ in range(2):
+        out = kernels.conv2d_fused(_t(x, cuda_device), (OC, C, 3, 3), _t(bias, cuda_device), cw, 1, 1,
+                                   in_kind=_ffi.IN_I32_CLAMP, out_kind=_ffi.OUT_F32 if out_f32 else _ffi.OUT_I32,
+                                   act_integer_bits=I, act_fraction_bits=F, relu=True, residual=_t(res, cuda_device),
+                                   round_f32=True)
+        assert np.array_equal(out.cpu().numpy(), want)
+    assert int(kernels.workspace(cuda_device).abs().sum()) == 0
