@@ -34,6 +34,7 @@ _SIGNATURES = {
     "ds_conv2d_i32": [_VP, _VP, _VP, _VP] + [_I] * 14 + [_VP],
     "ds_linear_ex": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, ctypes.POINTER(Fuse), _VP],
     "ds_conv2d_ex": [_VP, _VP, _VP, _VP] + [_I] * 13 + [ctypes.POINTER(Fuse), _VP],
+    "ds_conv2d_noalloc": [_VP, _VP, _VP, _VP] + [_I] * 13 + [ctypes.POINTER(Fuse), _VP],
     "ds_compress": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "ds_quantize_f32": [_VP, _VP, _LL, _I, _I, _I, _VP],
     "ds_maxpool2d_i32": [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],

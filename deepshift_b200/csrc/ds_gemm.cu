@@ -625,3 +625,53 @@ extern "C" int ds_conv2d_i32(const int32_t* x, const int32_t* packed, const int3
     f.act_bits = act_bits;
     return ds_conv2d_ex(x, packed, bias, out, B, C, H, W, OC, KH, KW, sh, sw, ph, pw, bits, base, &f, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Convolution entry point that allocates nothing, for callers that cannot call cudaMalloc.
+namespace {
+
+constexpr int kNoAllocMaxTiles = 16384;  // output tiles (256 rows x 128 or 64 columns) per call
+constexpr int kNoAllocMaxDevices = 64;
+
+// The split-K arrival counters of ds_conv2d_noalloc.  The array lives in the library image: every
+// GPU that loads the library holds these 64 KiB until the process exits.  In host code this name is
+// only a handle; the kernels need the device address, which cudaGetSymbolAddress gives per device.
+static __device__ __align__(256) int g_noalloc_counters[kNoAllocMaxTiles];
+
+int* g_noalloc_dev_ptr[kNoAllocMaxDevices];  // device address of the array, per device ordinal
+
+}  // namespace
+
+extern "C" int ds_conv2d_noalloc(const void* x, const int32_t* packed, const int32_t* bias, void* out, int B,
+                                 int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
+                                 int bits, int base, const ds_fuse_t* fuse, void* stream)
+{
+    if (B < 0 || C <= 0 || H <= 0 || W <= 0 || OC <= 0 || KH <= 0 || KW <= 0 || sh <= 0 || sw <= 0 ||
+        ph < 0 || pw < 0 || H + 2 * ph < KH || W + 2 * pw < KW)
+        return DS_ERR_BAD_ARG;
+    if (B == 0) return DS_OK;
+    const long long OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
+    const long long tiles = ((B * OH * OW + 255) / 256) * ((OC + (OC > 64 ? 127 : 63)) / (OC > 64 ? 128 : 64));
+    if (tiles > kNoAllocMaxTiles) return DS_ERR_SCRATCH;
+
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return DS_ERR_CUDA;
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return DS_ERR_UNSUPPORTED;
+    if (!g_noalloc_dev_ptr[dev]) {  // set-up: once per device, with that device current
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_counters) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return DS_ERR_CUDA;
+        }
+        g_noalloc_dev_ptr[dev] = static_cast<int*>(ptr);
+    }
+    int* counters = g_noalloc_dev_ptr[dev];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call (or an aborted one) left; the counters must start at 0.
+    if (cudaMemsetAsync(counters, 0, size_t(tiles) * sizeof(int), st) != cudaSuccess) return DS_ERR_CUDA;
+    ds_fuse_t f = {};
+    if (fuse) f = *fuse;
+    f.workspace = counters;
+    f.workspace_bytes = (long long)kNoAllocMaxTiles * (long long)sizeof(int);
+    return ds_conv2d_ex(x, packed, bias, out, B, C, H, W, OC, KH, KW, sh, sw, ph, pw, bits, base, &f, stream);
+}

@@ -218,6 +218,9 @@ const char* status_string(int s)
         case DS_ERR_CUDA: return "CUDA runtime error at launch";
         case DS_ERR_RANGE: return "size exceeds 32-bit indexing limits of this build";
         case DS_ERR_ALIGN: return "pointer not sufficiently aligned (outputs need 16 bytes)";
+        case DS_ERR_SCRATCH:
+            return "problem has more output tiles than the fixed scratch of the no-allocation entry point holds "
+                   "(16384 tiles of 256 positions x 128 channels)";
         default: return "unknown status";
     }
 }

@@ -38,7 +38,8 @@ typedef enum {
     DS_ERR_UNSUPPORTED = 2,  /* bits outside 1..7, base > 0, kernel window > 31, ...     */
     DS_ERR_CUDA = 3,         /* the CUDA runtime reported an error at launch              */
     DS_ERR_RANGE = 4,        /* a size exceeds what 32-bit indexing of this build allows  */
-    DS_ERR_ALIGN = 5         /* a pointer is not 16-byte aligned                          */
+    DS_ERR_ALIGN = 5,        /* a pointer is not 16-byte aligned                          */
+    DS_ERR_SCRATCH = 6       /* ds_conv2d_noalloc: more output tiles than its fixed scratch holds */
 } ds_status;
 
 /* Input element kinds of the *_ex entry points. */
@@ -118,6 +119,31 @@ int ds_linear_ex(const void *x, const int32_t *packed, const int32_t *bias, void
 int ds_conv2d_ex(const void *x, const int32_t *packed, const int32_t *bias, void *out, int B,
                  int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
                  int bits, int base, const ds_fuse_t *fuse, void *stream);
+
+/*
+ * ds_conv2d_ex for callers that must not allocate device memory (no counterpart in the reference).
+ *
+ * Who needs it: a host that has already handed all of the GPU's memory to its own pool or to other
+ * tenants, so that a cudaMalloc for the split-K counters could fail; or a latency-critical loop in
+ * which an allocation (and the device-wide synchronisation it can imply) is not acceptable and no
+ * pre-allocated workspace was threaded through to this call.
+ *
+ * Same arguments, result and bit-exactness as ds_conv2d_ex, except that fuse->workspace is ignored:
+ * the split-K arrival counters live in a fixed array inside the library (64 KiB on every GPU that
+ * loads the library, until the process exits).  The call itself and everything under it make no
+ * cudaMalloc / cudaFree and call no allocating library routine.
+ *   - Limit: at most 16384 output tiles per call, a tile being 256 output positions (b,oh,ow) by
+ *     128 output channels (64 when OC <= 64).  Larger problems return DS_ERR_SCRATCH and run nothing;
+ *     use ds_conv2d_ex with a workspace, or without one, for those.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - All calls on a device share the array.  Every call clears the counters it will use on
+ *     `stream` before its kernel, but two calls whose kernels overlap on the GPU (different streams,
+ *     no ordering between them) race on it: order such calls yourself.
+ */
+int ds_conv2d_noalloc(const void *x, const int32_t *packed, const int32_t *bias, void *out, int B,
+                      int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
+                      int bits, int base, const ds_fuse_t *fuse, void *stream);
 
 /*
  * Packs (shift', sign) into words.  Replaces COMPRESS_SIGN_SHIFT (shift_cuda.cpp:55-61 ->
