@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     for (int it = 0; it < my_tiles; ++it) {
         const int st = it & 1;
         if (!mbar_wait(&s.full[st], unsigned(it >> 1) & 1u)) bad = true;
-#pragma unroll 4
+#pragma unroll 8
         for (int k = 0; k < p.bk; ++k) {
             float a[kTM], b[TN];
             *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
