@@ -232,6 +232,10 @@ __device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
     else fn(std::integral_constant<int, INK_F32>());
 }
 
+// Small-batch linear layer (ds_small.cu): M <= 64 rows.  Exact integer path, optional split along
+// K with integer atomics when no epilogue is fused.
+int launch_small_linear(const GemmParams& p, cudaStream_t st);
+
 // Warp-specialised FP32-pipe kernel (ds_gemm_ws.cu).  am: AM_LINEAR, AM_TABLE or the window
 // width of the row mode.  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller then
 // falls back to the table mode or the integer path.
