@@ -119,11 +119,13 @@ def conv2d(input, shift, sign, bias=None, conc_weight=None, stride=1, padding=0,
         _check_tensor(bias, "bias", torch.int32)
     B, C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW = _conv_geometry(input, shift, stride, padding, dilation, groups)
     out = torch.empty([B, OC, OH, OW], dtype=torch.int32, device=input.device)
+    # ds_conv2d_i32 plus the split-K counter workspace (layers with few output tiles)
+    f = _fuse(act_bits=act_bits, workspace=workspace(input.device))
     with torch.cuda.device(input.device):
-        rc = _ffi.lib().ds_conv2d_i32(input.data_ptr(), conc_weight.data.data_ptr(),
-                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                                      B, C, H, W, OC, KH, KW, sh, sw, ph, pw, conc_weight.bits,
-                                      conc_weight.base, int(act_bits), _stream_ptr(input.device))
+        rc = _ffi.lib().ds_conv2d_ex(input.data_ptr(), conc_weight.data.data_ptr(),
+                                     bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                     B, C, H, W, OC, KH, KW, sh, sw, ph, pw, conc_weight.bits,
+                                     conc_weight.base, f, _stream_ptr(input.device))
     _ffi.check(rc, "conv2d")
     return out
 
