@@ -32,6 +32,7 @@ struct GemmParams {
     // fused prologue / epilogue
     int in_kind, out_kind, relu, requant, round_f32;
     // split-K (warp-specialised kernel): gridDim.z CTAs share one output tile
+    int grid_m, grid_n;  // output tiles along M and N
     int splits;          // 1 = off
     int tiles_per_split; // k-tiles per split
     int* counters;       // one arrival counter per output tile, zero between launches

@@ -47,7 +47,10 @@ struct WsSmem {
     alignas(8) unsigned long long full[WS_STAGES];
     alignas(8) unsigned long long empty[WS_STAGES];
     int lut0[256];  // float bits of the decoded weight per field value
-    int negc[BN];   // negative weights per output column
+    // Negative weights per output column.  Four sets, used round-robin by item: the producers can
+    // be two items ahead of the consumers (items of a single k-tile), and a set is cleared by the
+    // consumers only after their epilogue.
+    int negc[4][BN];
     int err;
     int last_flag;  // split-K: this CTA arrived last at its tile's counter
     int accs[kTM * TN * WS_CONS];  // drained accumulators, [slot][consumer thread]
@@ -89,6 +92,27 @@ __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 2, %0;" 
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(WS_PROD) : "memory"); }
 
 // ---------------------------------------------------------------------------------------------
+// Work item = (output tile, K split).  Items are numbered with the row tile fastest, so CTAs that
+// run side by side share weight tiles in L2.
+struct WsItem {
+    int m0, n0, t_begin, t_end, tile_id;
+};
+
+__device__ __forceinline__ WsItem ws_item(const GemmParams& p, int item, int BM, int BN)
+{
+    WsItem w;
+    const int mt = item % p.grid_m;
+    const int rest = item / p.grid_m;
+    const int nt = rest % p.grid_n;
+    const int sp = rest / p.grid_n;
+    w.m0 = mt * BM;
+    w.n0 = nt * BN;
+    w.t_begin = sp * p.tiles_per_split;
+    w.t_end = min(p.ntiles, w.t_begin + p.tiles_per_split);
+    w.tile_id = nt * p.grid_m + mt;
+    return w;
+}
+
 template <int TN, int AM>
 __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 {
@@ -104,23 +128,14 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     S& s = *reinterpret_cast<S*>(smem_raw);
 
     const int t = threadIdx.x;
-    const int m0 = blockIdx.x * BM;
-    const int n0 = blockIdx.y * BN;
-    // split-K: this CTA handles k-tiles [t_begin, t_end)
-    const int t_begin = blockIdx.z * p.tiles_per_split;
-    const int t_end = min(p.ntiles, t_begin + p.tiles_per_split);
-    const int my_tiles = t_end - t_begin;
+    const int total_items = p.grid_m * p.grid_n * p.splits;
 
-    // ---- set-up by all 640 threads ----------------------------------------------------------------
+    // ---- set-up by all threads ------------------------------------------------------------------
     for (int f = t; f < (1 << p.dec.fw); f += WS_NT) {
         int neg;
         s.lut0[f] = __float_as_int(decode_f32(uint32_t(f), p.dec, true, neg));
     }
-    for (int i = t; i < BN; i += WS_NT) s.negc[i] = 0;
-    if (t < WS_CONS) {
-#pragma unroll
-        for (int q = 0; q < kTM * TN; ++q) s.accs[q * WS_CONS + t] = 0;
-    }
+    for (int i = t; i < 4 * BN; i += WS_NT) (&s.negc[0][0])[i] = 0;
     if (t == 0) {
         for (int i = 0; i < WS_STAGES; ++i) {
             mbar_init(&s.full[i], WS_PROD);
@@ -134,32 +149,13 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // =========================== producers ==================================================
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_PROD_REGS));
         const int pt = t - WS_CONS;
-        constexpr int PIX = BM / WS_PROD;  // 2 rows of the x tile per producer thread (conv)
+        constexpr int PIX = BM / WS_PROD;  // rows of the x tile per producer thread (conv)
         const char* x_pix[PIX];
         uint32_t rowmask[PIX], colmask[PIX];
-        if (CONV) {
-#pragma unroll
-            for (int q = 0; q < PIX; ++q) {
-                const int m = m0 + pt + q * WS_PROD;
-                x_pix[q] = reinterpret_cast<const char*>(p.x);
-                rowmask[q] = colmask[q] = 0;
-                if (m < p.M) {
-                    const int b = m / p.P, pp = m - b * p.P;
-                    const int oh = pp / p.OW, ow = pp - oh * p.OW;
-                    const int ih0 = oh * p.sh - p.ph, iw0 = ow * p.sw - p.pw;
-                    for (int kh = 0; kh < p.KH; ++kh)
-                        if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[q] |= 1u << kh;
-                    for (int kw = 0; kw < p.KW; ++kw)
-                        if (unsigned(iw0 + kw) < unsigned(p.W)) colmask[q] |= 1u << kw;
-                    // address of (b, 0, ih0, iw0): may lie outside the tensor, only valid taps are read
-                    x_pix[q] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4;
-                }
-            }
-        }
         // weight words: column n = wi % BN, word jw = wi / BN of the k-tile, wi = pt + WS_PROD * e
         constexpr int EW = (BN * (WS_BKT / 4) + WS_PROD - 1) / WS_PROD;
         const int wn = pt & (BN - 1);
-        const int32_t* wrow = (n0 + wn < p.N) ? p.packed + (long long)(n0 + wn) * p.dec.row_len : nullptr;
+        const int32_t* wrow = nullptr;
         const uint32_t fmask = (1u << p.dec.fw) - 1u;
 
         // Registers that hold one k-tile of this thread's x values and weight words between the
@@ -172,6 +168,30 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         int xr[XREG];
         uint32_t w_reg[EW];
         static_assert(XREG <= 32, "producer registers");
+
+        // Per-item state of this thread: the x rows it gathers and the weight row it decodes.
+        auto setup_item = [&](const WsItem& w) {
+            wrow = (w.n0 + wn < p.N) ? p.packed + (long long)(w.n0 + wn) * p.dec.row_len : nullptr;
+            if (CONV) {
+#pragma unroll
+                for (int q = 0; q < PIX; ++q) {
+                    const int m = w.m0 + pt + q * WS_PROD;
+                    x_pix[q] = reinterpret_cast<const char*>(p.x);
+                    rowmask[q] = colmask[q] = 0;
+                    if (m < p.M) {
+                        const int b = m / p.P, pp = m - b * p.P;
+                        const int oh = pp / p.OW, ow = pp - oh * p.OW;
+                        const int ih0 = oh * p.sh - p.ph, iw0 = ow * p.sw - p.pw;
+                        for (int kh = 0; kh < p.KH; ++kh)
+                            if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[q] |= 1u << kh;
+                        for (int kw = 0; kw < p.KW; ++kw)
+                            if (unsigned(iw0 + kw) < unsigned(p.W)) colmask[q] |= 1u << kw;
+                        // address of (b, 0, ih0, iw0): may lie outside the tensor, only valid taps are read
+                        x_pix[q] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4;
+                    }
+                }
+            }
+        };
 
         auto fill_table = [&](int tile) {
             if (!CONV || pt >= WS_BKT) return;
@@ -202,7 +222,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 
         // Issues the global loads of one k-tile into registers.  Positions outside the image or
         // the matrix get `padv` (0, or the marker that stands for an unquantised 0 for fp32 kinds).
-        auto issue_loads = [&](int tile) {
+        auto issue_loads = [&](int tile, int m0) {
             const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
             const int w0 = tile * p.kt_words;
 #pragma unroll
@@ -304,8 +324,8 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // Decodes this thread's weight words through the table into stage `st`.  Slots k >= K of
         // the last words decode like any field (a zero field is -2^0); the x values stored there
         // are 0, so they add nothing, and the epilogue takes their share (tail_neg) out of the
-        // negative-weight count.
-        auto store_w = [&](auto num_tag, int st) {
+        // negative-weight count `negc` of the item.
+        auto store_w = [&](auto num_tag, int st, int* negc) {
             constexpr int NUM = decltype(num_tag)::value;
             int negs = 0;
 #pragma unroll
@@ -323,37 +343,52 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     }
                 }
             }
-            if (negs) atomicAdd(&s.negc[wn], negs);
+            if (negs) atomicAdd(&negc[wn], negs);
         };
 
-        // Loads run one k-tile ahead of the stores: while this thread waits for a free stage, the
-        // loads of the tile it will store next are already in flight.
-        fill_table(t_begin);
-        if (CONV) producer_bar();
-        issue_loads(t_begin);
-        for (int it = 0; it < my_tiles; ++it) {
-            const int tile = t_begin + it;
-            const int st = it & 1;
-            if (it >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned((it >> 1) - 1) & 1u)) s.err = 1;
-            const int k0 = tile * p.bk;
-            const bool last = tile + 1 >= p.ntiles;
-            with_input_kind(p, [&](auto ink_tag) {
-                if (last) store_x(ink_tag, std::true_type(), st, k0);
-                else store_x(ink_tag, std::false_type(), st, k0);
-            });
-            switch (p.dec.num) {
-                case 4: store_w(std::integral_constant<int, 4>(), st); break;
-                case 5: store_w(std::integral_constant<int, 5>(), st); break;
-                case 6: store_w(std::integral_constant<int, 6>(), st); break;
-                case 8: store_w(std::integral_constant<int, 8>(), st); break;
-                case 10: store_w(std::integral_constant<int, 10>(), st); break;
-                default: store_w(std::integral_constant<int, 16>(), st); break;
-            }
-            mbar_arrive(&s.full[st]);
-            if (it + 1 < my_tiles) {
-                fill_table(tile + 1);
+        // The CTA walks its items; within an item the k-tiles.  Loads run one k-tile ahead of the
+        // stores -- also across item boundaries: while the consumers finish an output tile and run
+        // its epilogue, the first k-tiles of the next item are already being staged.
+        int item = blockIdx.x, seq = 0, git = 0;
+        if (item < total_items) {
+            WsItem cur = ws_item(p, item, BM, BN);
+            int tile = cur.t_begin;
+            setup_item(cur);
+            fill_table(tile);
+            if (CONV) producer_bar();
+            issue_loads(tile, cur.m0);
+            while (true) {
+                const int st = git % WS_STAGES;
+                if (git >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u)) s.err = 1;
+                const int k0 = tile * p.bk;
+                const bool last = tile + 1 >= p.ntiles;
+                with_input_kind(p, [&](auto ink_tag) {
+                    if (last) store_x(ink_tag, std::true_type(), st, k0);
+                    else store_x(ink_tag, std::false_type(), st, k0);
+                });
+                int* negc = s.negc[seq & 3];
+                switch (p.dec.num) {
+                    case 4: store_w(std::integral_constant<int, 4>(), st, negc); break;
+                    case 5: store_w(std::integral_constant<int, 5>(), st, negc); break;
+                    case 6: store_w(std::integral_constant<int, 6>(), st, negc); break;
+                    case 8: store_w(std::integral_constant<int, 8>(), st, negc); break;
+                    case 10: store_w(std::integral_constant<int, 10>(), st, negc); break;
+                    default: store_w(std::integral_constant<int, 16>(), st, negc); break;
+                }
+                mbar_arrive(&s.full[st]);
+                ++git;
+                // next (item, k-tile)
+                if (++tile >= cur.t_end) {
+                    item += gridDim.x;
+                    if (item >= total_items) break;
+                    ++seq;
+                    cur = ws_item(p, item, BM, BN);
+                    tile = cur.t_begin;
+                    setup_item(cur);
+                }
+                fill_table(tile);
                 if (CONV) producer_bar();
-                issue_loads(tile + 1);
+                issue_loads(tile, cur.m0);
             }
         }
         if (s.err) g_ws_error = 1;
@@ -375,77 +410,98 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         tm = (warp / WNG) * 4 + (lane >> 3);
     }
     float accf[kTM][TN];
-#pragma unroll
-    for (int i = 0; i < kTM; ++i)
-#pragma unroll
-        for (int j = 0; j < TN; ++j) accf[i][j] = kMagic;
-
-    int ndrains = 0, since = 0;
     bool bad = false;
-    for (int it = 0; it < my_tiles; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&s.full[st], unsigned(it >> 1) & 1u)) bad = true;
+    int git = 0, seq = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++seq) {
+        const WsItem cur = ws_item(p, item, BM, BN);
+        const int my_tiles = cur.t_end - cur.t_begin;
+#pragma unroll
+        for (int i = 0; i < kTM; ++i)
+#pragma unroll
+            for (int j = 0; j < TN; ++j) accf[i][j] = kMagic;
+        int ndrains = 0, since = 0;
+        for (int it = 0; it < my_tiles; ++it, ++git) {
+            const int st = git % WS_STAGES;
+            if (!mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u)) bad = true;
 #pragma unroll 8
-        for (int k = 0; k < p.bk; ++k) {
-            float a[kTM], b[TN];
-            *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
-            *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&s.a[st][k][BM / 2 + 4 * tm]);
-            *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s.b[st][k][4 * tn]);
-            if (TN == 8)
-                *reinterpret_cast<float4*>(&b[TN - 4]) = *reinterpret_cast<const float4*>(&s.b[st][k][BN / 2 + 4 * tn]);
+            for (int k = 0; k < p.bk; ++k) {
+                float a[kTM], b[TN];
+                *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
+                *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&s.a[st][k][BM / 2 + 4 * tm]);
+                *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s.b[st][k][4 * tn]);
+                if (TN == 8)
+                    *reinterpret_cast<float4*>(&b[TN - 4]) = *reinterpret_cast<const float4*>(&s.b[st][k][BN / 2 + 4 * tn]);
 #pragma unroll
-            for (int i = 0; i < kTM; ++i)
+                for (int i = 0; i < kTM; ++i)
 #pragma unroll
-                for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
-        }
-        mbar_arrive(&s.empty[st]);
-        if (++since == p.flush_tiles || it + 1 == my_tiles) {
-            // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
-            // slots and restart them; the epilogue removes ndrains * kMagicBits.
+                    for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
+            }
+            mbar_arrive(&s.empty[st]);
+            if (++since == p.flush_tiles || it + 1 == my_tiles) {
+                // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
+                // slots and restart them; the epilogue removes ndrains * kMagicBits.  The first
+                // drain of an item overwrites what the previous item left in the slots.
+                if (ndrains == 0) {
 #pragma unroll
-            for (int i = 0; i < kTM; ++i)
+                    for (int i = 0; i < kTM; ++i)
 #pragma unroll
-                for (int j = 0; j < TN; ++j) {
-                    red_shared_add(&s.accs[(i * TN + j) * WS_CONS + t], __float_as_int(accf[i][j]));
-                    accf[i][j] = kMagic;
+                        for (int j = 0; j < TN; ++j) {
+                            s.accs[(i * TN + j) * WS_CONS + t] = __float_as_int(accf[i][j]);
+                            accf[i][j] = kMagic;
+                        }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j) {
+                            red_shared_add(&s.accs[(i * TN + j) * WS_CONS + t], __float_as_int(accf[i][j]));
+                            accf[i][j] = kMagic;
+                        }
                 }
-            ++ndrains;
-            since = 0;
+                ++ndrains;
+                since = 0;
+            }
         }
+
+        // ---- epilogue of the item ----------------------------------------------------------------
+        const int* negc = s.negc[seq & 3];
+        // tail_neg belongs to the split that holds the last k-tile
+        const int tailc = (cur.t_end == p.ntiles) ? p.tail_neg : 0;
+        auto part = [&](int i, int j, long long) -> int {
+            return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits;
+        };
+        if (p.splits == 1) {
+            store_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part,
+                                 [&](int col) -> int { return negc[col] - tailc; });
+        } else {
+            // split-K: add the partial sums into the zeroed output; the CTA that arrives last at
+            // this tile's counter reads the totals back and applies the epilogue in place.
+            reduce_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part,
+                                  [&](int col) -> int { return negc[col] - tailc; });
+            __threadfence();
+            consumer_bar();
+            if (t == 0) {
+                int* cnt = p.counters + cur.tile_id;
+                const int prev = atomicAdd(cnt, 1);
+                const int lastone = (prev == p.splits - 1);
+                if (lastone) *cnt = 0;  // ready for the next launch
+                s.last_flag = lastone;
+            }
+            consumer_bar();
+            if (s.last_flag) {
+                __threadfence();
+                const int* tot = static_cast<const int*>(p.out);
+                store_tile<TN, CONV>(
+                    p, cur.m0, cur.n0, tm, tn, BM, BN, [&](int, int, long long o) -> int { return __ldcg(tot + o); },
+                    [&](int) -> int { return 0; });
+            }
+        }
+        // All consumers have read this item's negative-weight counts before they are cleared for
+        // a later item (the producers are filling other sets meanwhile).
+        consumer_bar();
+        for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
     }
     if (bad) g_ws_error = 1;
-
-    // tail_neg belongs to the split that holds the last k-tile
-    const int tailc = (t_end == p.ntiles) ? p.tail_neg : 0;
-    if (p.splits == 1) {
-        store_tile<TN, CONV>(
-            p, m0, n0, tm, tn, BM, BN,
-            [&](int i, int j, long long) -> int { return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits; },
-            [&](int col) -> int { return s.negc[col] - tailc; });
-        return;
-    }
-    // ---- split-K: add the partial sums into the zeroed output, then the CTA that arrives last at
-    // this tile's counter reads the totals back and applies the epilogue in place.
-    reduce_tile<TN, CONV>(
-        p, m0, n0, tm, tn, BM, BN,
-        [&](int i, int j, long long) -> int { return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits; },
-        [&](int col) -> int { return s.negc[col] - tailc; });
-    __threadfence();
-    consumer_bar();
-    if (t == 0) {
-        int* cnt = p.counters + (blockIdx.y * gridDim.x + blockIdx.x);
-        const int prev = atomicAdd(cnt, 1);
-        const int lastone = (prev == p.splits - 1);
-        if (lastone) *cnt = 0;  // ready for the next launch
-        s.last_flag = lastone;
-    }
-    consumer_bar();
-    if (!s.last_flag) return;
-    __threadfence();
-    const int* tot = static_cast<const int*>(p.out);
-    store_tile<TN, CONV>(
-        p, m0, n0, tm, tn, BM, BN, [&](int, int, long long o) -> int { return __ldcg(tot + o); },
-        [&](int) -> int { return 0; });
 }
 
 // Chooses the k-tile: a multiple of num (whole packed words) and of the staging granularity
@@ -470,6 +526,18 @@ bool ws_choose_tile(GemmParams& p)
     return p.flush_tiles >= 1;
 }
 
+int num_sms()
+{
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
 template <int TN, int AM>
 int ws_launch_cfg(GemmParams p, cudaStream_t st)
 {
@@ -491,20 +559,14 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     }
     if (attr_state < 0) return DS_ERR_UNSUPPORTED;
     const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
-    if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
+    if (gx * gy > 500000000LL) return DS_ERR_RANGE;
     // Split-K when the output tiles alone fill the SMs badly (few tiles, or a last wave that is
     // mostly empty) and the caller gave a counter workspace: gridDim.z CTAs share a tile.
     p.splits = 1;
     p.tiles_per_split = p.ntiles;
     const long long tiles = gx * gy;
     if (p.counters && tiles <= p.counter_slots && p.ntiles >= 16) {
-        static int sms = 0;
-        if (!sms) {
-            int dev = 0;
-            if (cudaGetDevice(&dev) != cudaSuccess ||
-                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-                sms = 148;
-        }
+        const int sms = num_sms();
         auto eff = [&](int sp) {
             const long long ctas = tiles * sp, waves = (ctas + sms - 1) / sms;
             return double(ctas) / double(waves * sms);
@@ -524,7 +586,10 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
             if (cudaMemsetAsync(p.out, 0, size_t(p.M) * size_t(p.N) * 4, st) != cudaSuccess) return DS_ERR_CUDA;
         }
     }
-    kern<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)p.splits), WS_NT, smem, st>>>(p);
+    p.grid_m = int(gx);
+    p.grid_n = int(gy);
+    const long long items = tiles * p.splits;
+    kern<<<dim3((unsigned)(items < num_sms() ? items : num_sms())), WS_NT, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
