@@ -328,3 +328,90 @@ def test_conv_split_k_with_workspace(oracle, cuda_device, out_f32):
                                    round_f32=True)
         assert np.array_equal(out.cpu().numpy(), want)
     assert int(kernels.workspace(cuda_device).abs().sum()) == 0
+
+
+def test_plain_c_abi_entry_points(oracle, cuda_device):
+    """ds_linear_i32 / ds_conv2d_i32 called directly with raw pointers, as a foreign-language
+    binding would (no fused options, no workspace)."""
+    from deepshift_b200 import _ffi
+    lib = _ffi.lib()
+    rng = np.random.default_rng(31)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    x = acts_q16(rng, (100, 260))
+    shift, sign = weights(rng, (70, 260))
+    bias = rng.integers(-2000, 2000, 70).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    xt, bt = _t(x, cuda_device), _t(bias, cuda_device)
+    out = torch.empty((100, 70), dtype=torch.int32, device=cuda_device)
+    for act_bits in (0, 16):
+        out.fill_(-1)
+        assert lib.ds_linear_i32(xt.data_ptr(), cw.data.data_ptr(), bt.data_ptr(), out.data_ptr(), 100, 260, 70,
+                                 cw.bits, cw.base, act_bits, stream) == 0
+        assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, bias))
+    x = acts_q16(rng, (6, 32, 14, 14))
+    shift, sign = weights(rng, (200, 32, 3, 3))
+    bias = rng.integers(-2000, 2000, 200).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    xt, bt = _t(x, cuda_device), _t(bias, cuda_device)
+    ref = oracle.conv2d(x, shift, sign, bias, (2, 2), (1, 1))
+    out = torch.empty(ref.shape, dtype=torch.int32, device=cuda_device)
+    for act_bits in (0, 16):
+        out.fill_(-1)
+        assert lib.ds_conv2d_i32(xt.data_ptr(), cw.data.data_ptr(), bt.data_ptr(), out.data_ptr(), 6, 32, 14, 14, 200,
+                                 3, 3, 2, 2, 1, 1, cw.bits, cw.base, act_bits, stream) == 0
+        assert np.array_equal(out.cpu().numpy(), ref)
+    # misaligned output pointer is refused
+    assert lib.ds_conv2d_i32(xt.data_ptr(), cw.data.data_ptr(), None, out.data_ptr() + 4, 6, 32, 14, 14, 200, 3, 3, 2, 2,
+                             1, 1, cw.bits, cw.base, 0, stream) == 5
+
+
+def test_many_items_per_cta_and_single_tile_items(oracle, cuda_device):
+    """More output tiles than SMs (each persistent CTA walks several items) with K so short that an
+    item is a single k-tile: the producers run two items ahead of the consumers."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(41)
+    B, C, H, OC = 700, 1, 12, 20   # M = 700 * 64 = 44800 rows -> 175 tiles, K = 25
+    x = acts_q16(rng, (B, C, H, H))
+    shift, sign = weights(rng, (OC, C, 5, 5))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                         _cw(shift, sign, cuda_device), 1, 0, act_bits=16)
+    assert np.array_equal(out.cpu().numpy(), oracle.conv2d(x, shift, sign, bias, (1, 1), (0, 0)))
+
+
+def test_random_shapes_against_oracle(oracle, cuda_device):
+    """Seeded random convolution and linear shapes (ragged sizes, odd windows, strides, paddings,
+    every field width), both arithmetic paths, fused and plain entry points."""
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(2025)
+    for case in range(60):
+        lo = int(rng.choice([-1, -3, -7, -15]))
+        zeros = bool(rng.integers(0, 2))
+        act_bits = int(rng.choice([0, 16]))
+        if case % 3 == 0:
+            M, K, N = int(rng.integers(1, 400)), int(rng.integers(1, 700)), int(rng.integers(1, 300))
+            x = acts_q16(rng, (M, K))
+            shift, sign = weights(rng, (N, K), lo, zeros)
+            bias = rng.integers(-2000, 2000, N).astype(np.int32)
+            out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                                 _cw(shift, sign, cuda_device), act_bits=act_bits)
+            assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, bias)), (case, M, K, N, lo, zeros)
+            continue
+        B, C, OC = int(rng.integers(1, 40)), int(rng.integers(1, 70)), int(rng.integers(1, 200))
+        kh, kw = int(rng.integers(1, 6)), int(rng.choice([1, 2, 3, 5, 7]))
+        sh, sw = int(rng.integers(1, 3)), int(rng.integers(1, 3))
+        ph, pw = int(rng.integers(0, kh)), int(rng.integers(0, kw))
+        H, W = int(rng.integers(kh, kh + 20)), int(rng.integers(kw, kw + 20))
+        x = acts_q16(rng, (B, C, H, W))
+        shift, sign = weights(rng, (OC, C, kh, kw), lo, zeros)
+        bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+        ref = oracle.conv2d(x, shift, sign, bias, (sh, sw), (ph, pw))
+        cw = _cw(shift, sign, cuda_device)
+        tag = (case, B, C, H, W, OC, kh, kw, sh, sw, ph, pw, lo, zeros, act_bits)
+        out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device), cw, (sh, sw),
+                             (ph, pw), act_bits=act_bits)
+        assert np.array_equal(out.cpu().numpy(), ref), tag
+        out = kernels.conv2d_fused(_t(x, cuda_device), (OC, C, kh, kw), _t(bias, cuda_device), cw, (sh, sw), (ph, pw),
+                                   in_kind=_ffi.IN_I32_CLAMP, out_kind=_ffi.OUT_F32, act_integer_bits=4,
+                                   act_fraction_bits=12, relu=True)
+        assert np.array_equal(out.cpu().numpy(), oracle.from_fixed(np.maximum(ref, 0), 12)), tag
