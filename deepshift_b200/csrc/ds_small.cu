@@ -14,16 +14,17 @@ namespace {
 
 constexpr int SM_THREADS = 256;
 
-template <int MT>
+// MT rows x NTILE columns per CTA, CPT columns per thread (256 threads).
+template <int MT, int CPT>
 struct SmallCfg {
-    static constexpr int NTILE = 1024 / MT;          // columns per CTA
-    static constexpr int KC = (MT >= 16) ? 32 : 16;  // k values per chunk
+    static constexpr int NTILE = SM_THREADS / MT * CPT;
+    static constexpr int KC = (NTILE > 64) ? 16 : 32;  // k values per chunk
 };
 
-template <int MT>
+template <int MT, int CPT>
 __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmParams p, int chunks_per_split)
 {
-    using Cfg = SmallCfg<MT>;
+    using Cfg = SmallCfg<MT, CPT>;
     constexpr int NTILE = Cfg::NTILE, KC = Cfg::KC;
     __shared__ int xs[MT][KC];
     __shared__ __align__(16) int2 wv[KC][NTILE];
@@ -37,8 +38,10 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
         lut_s[f] = shv;
         lut_m[f] = mul;
     }
-    const int tm = t / (NTILE / 4), tn = t % (NTILE / 4);
-    int acc[4] = {0, 0, 0, 0};
+    const int tm = t / (NTILE / CPT), tn = t % (NTILE / CPT);
+    int acc[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) acc[j] = 0;
     const uint32_t fmask = (1u << p.dec.fw) - 1u;
     const int nchunks = (p.K + KC - 1) / KC;
     const int c_begin = blockIdx.z * chunks_per_split;
@@ -77,12 +80,11 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
 #pragma unroll 4
         for (int kl = 0; kl < KC; ++kl) {
             const int xv = xs[tm][kl];
-            const int4 w01 = *reinterpret_cast<const int4*>(&wv[kl][4 * tn]);
-            const int4 w23 = *reinterpret_cast<const int4*>(&wv[kl][4 * tn + 2]);
-            acc[0] += (xv >> w01.x) * w01.y;
-            acc[1] += (xv >> w01.z) * w01.w;
-            acc[2] += (xv >> w23.x) * w23.y;
-            acc[3] += (xv >> w23.z) * w23.w;
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                const int2 w = wv[kl][CPT * tn + j];
+                acc[j] += (xv >> w.x) * w.y;
+            }
         }
         __syncthreads();
     }
@@ -90,8 +92,8 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
     const int m = m0 + tm;
     if (m >= p.M) return;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int n = n0 + 4 * tn + j;
+    for (int j = 0; j < CPT; ++j) {
+        const int n = n0 + CPT * tn + j;
         if (n >= p.N) continue;
         const long long o = (long long)m * p.N + n;
         int v = acc[j];
@@ -110,10 +112,10 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
     }
 }
 
-template <int MT>
+template <int MT, int CPT>
 int launch_small(const GemmParams& p, cudaStream_t st)
 {
-    using Cfg = SmallCfg<MT>;
+    using Cfg = SmallCfg<MT, CPT>;
     const int gx = (p.N + Cfg::NTILE - 1) / Cfg::NTILE, gy = (p.M + MT - 1) / MT;
     const int nchunks = (p.K + Cfg::KC - 1) / Cfg::KC;
     const bool plain = p.out_kind == DS_OUT_I32 && !p.relu && !p.requant && !p.round_f32 && !p.residual;
@@ -124,7 +126,7 @@ int launch_small(const GemmParams& p, cudaStream_t st)
     int per = (nchunks + splits - 1) / splits;
     splits = (nchunks + per - 1) / per;
     if (splits > 1 && cudaMemsetAsync(p.out, 0, size_t(p.M) * size_t(p.N) * 4, st) != cudaSuccess) return DS_ERR_CUDA;
-    small_linear_kernel<MT><<<dim3(gx, gy, splits), SM_THREADS, 0, st>>>(p, per);
+    small_linear_kernel<MT, CPT><<<dim3(gx, gy, splits), SM_THREADS, 0, st>>>(p, per);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
@@ -133,7 +135,10 @@ int launch_small(const GemmParams& p, cudaStream_t st)
 int launch_small_linear(const GemmParams& p, cudaStream_t st)
 {
     if (p.N > 65535 * 64) return DS_ERR_RANGE;
-    return p.M <= 4 ? launch_small<4>(p, st) : launch_small<16>(p, st);
+    if (p.M <= 4) return launch_small<4, 4>(p, st);
+    // few columns: one column per thread, four times as many CTAs
+    const long long ctas4 = (long long)((p.N + 63) / 64) * ((p.M + 15) / 16);
+    return ctas4 >= 148 ? launch_small<16, 4>(p, st) : launch_small<16, 1>(p, st);
 }
 
 }  // namespace ds
