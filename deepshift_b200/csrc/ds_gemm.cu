@@ -514,8 +514,19 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.requant = f.requant;
     p.round_f32 = f.round_f32;
     p.splits = 1;
+    // workspace: kWorkspaceCounters arrival counters, then (optionally) room for partial sums
     p.counters = static_cast<int*>(f.workspace);
     p.counter_slots = f.workspace ? f.workspace_bytes / 4 : 0;
+    p.partials = nullptr;
+    p.partial_bytes = 0;
+    if (p.counter_slots > kWorkspaceCounters) {
+        p.partials = p.counters + kWorkspaceCounters;
+        p.partial_bytes = f.workspace_bytes - (long long)kWorkspaceCounters * 4;
+        p.counter_slots = kWorkspaceCounters;
+    }
+    p.full_units = p.tail_first = p.tail_items = 0;
+    p.tail_splits = 1;
+    p.tail_tps = 0;
     if (f.workspace && ((reinterpret_cast<uintptr_t>(f.workspace) & 3u) || f.workspace_bytes < 0)) return DS_ERR_BAD_ARG;
     p.residual = f.residual;
     p.q.scale = float(1ll << (needs_if ? F : 0));

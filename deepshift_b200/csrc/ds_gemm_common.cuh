@@ -37,10 +37,22 @@ struct GemmParams {
     int tiles_per_split; // k-tiles per split
     int* counters;       // one arrival counter per output tile, zero between launches
     long long counter_slots;
+    // tail split (warp-specialised kernel): the output tiles that would form a last, mostly empty
+    // wave are each shared by tail_splits CTAs, which exchange partial sums through `partials`
+    int full_units;      // work units before the tail: grid_m * grid_n * splits, or the full waves
+    int tail_first;      // first output tile of the tail
+    int tail_items;      // output tiles in the tail, 0 = off
+    int tail_splits;
+    int tail_tps;        // k-tiles per tail split
+    int* partials;       // [tail item][split][kTM * TN][consumer thread]
+    long long partial_bytes;
     Quant q;
     int rq_lo, rq_hi;
     float inv_scale;  // 2^-F
 };
+
+// Leading int32 slots of a caller's workspace that hold arrival counters; partial sums follow.
+constexpr int kWorkspaceCounters = 16384;
 
 struct alignas(16) KEntry {
     int off;  // byte offset of the tap (table mode) or of the row start (row mode)

@@ -92,24 +92,40 @@ __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 2, %0;" 
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(WS_PROD) : "memory"); }
 
 // ---------------------------------------------------------------------------------------------
-// Work item = (output tile, K split).  Items are numbered with the row tile fastest, so CTAs that
-// run side by side share weight tiles in L2.
+// Work unit = (output tile, K range).  Units are numbered with the row tile fastest, so CTAs that
+// run side by side share weight tiles in L2.  Units [0, full_units) cover every output tile
+// `splits` times (1 = each tile whole); the units after them are the tail: the last tail_items
+// tiles, each cut into tail_splits K ranges so that the last wave of CTAs is short instead of
+// mostly empty.
 struct WsItem {
     int m0, n0, t_begin, t_end, tile_id;
+    int tail_idx;  // >= 0: tail unit of that tail tile, partial sums go through the workspace
+    int sp;
 };
 
-__device__ __forceinline__ WsItem ws_item(const GemmParams& p, int item, int BM, int BN)
+__device__ __forceinline__ WsItem ws_item(const GemmParams& p, int unit, int BM, int BN)
 {
     WsItem w;
-    const int mt = item % p.grid_m;
-    const int rest = item / p.grid_m;
-    const int nt = rest % p.grid_n;
-    const int sp = rest / p.grid_n;
+    int tile, tps;
+    if (unit < p.full_units) {
+        const int tiles = p.grid_m * p.grid_n;
+        w.sp = unit / tiles;
+        tile = unit - w.sp * tiles;
+        tps = p.tiles_per_split;
+        w.tail_idx = -1;
+    } else {
+        const int v = unit - p.full_units;
+        w.sp = v / p.tail_items;
+        w.tail_idx = v - w.sp * p.tail_items;
+        tile = p.tail_first + w.tail_idx;
+        tps = p.tail_tps;
+    }
+    const int nt = tile / p.grid_m, mt = tile - nt * p.grid_m;
     w.m0 = mt * BM;
     w.n0 = nt * BN;
-    w.t_begin = sp * p.tiles_per_split;
-    w.t_end = min(p.ntiles, w.t_begin + p.tiles_per_split);
-    w.tile_id = nt * p.grid_m + mt;
+    w.t_begin = w.sp * tps;
+    w.t_end = min(p.ntiles, w.t_begin + tps);
+    w.tile_id = tile;
     return w;
 }
 
@@ -128,7 +144,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     S& s = *reinterpret_cast<S*>(smem_raw);
 
     const int t = threadIdx.x;
-    const int total_items = p.grid_m * p.grid_n * p.splits;
+    const int total_items = p.full_units + p.tail_items * p.tail_splits;
 
     // ---- set-up by all threads ------------------------------------------------------------------
     for (int f = t; f < (1 << p.dec.fw); f += WS_NT) {
@@ -423,19 +439,28 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         for (int it = 0; it < my_tiles; ++it, ++git) {
             const int st = git % WS_STAGES;
             if (!mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u)) bad = true;
-#pragma unroll 8
-            for (int k = 0; k < p.bk; ++k) {
-                float a[kTM], b[TN];
-                *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
-                *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&s.a[st][k][BM / 2 + 4 * tm]);
-                *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s.b[st][k][4 * tn]);
-                if (TN == 8)
-                    *reinterpret_cast<float4*>(&b[TN - 4]) = *reinterpret_cast<const float4*>(&s.b[st][k][BN / 2 + 4 * tn]);
+            // The k-tile sizes of 3x3, 1x1 / 7x7 and 5x5 windows get fully unrolled loops.
+            auto k_loop = [&](auto bk_tag) {
+                constexpr int CBK = decltype(bk_tag)::value;
+                const int nk = CBK ? CBK : p.bk;
+#pragma unroll(CBK ? CBK : 8)
+                for (int k = 0; k < nk; ++k) {
+                    float a[kTM], b[TN];
+                    *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
+                    *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&s.a[st][k][BM / 2 + 4 * tm]);
+                    *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s.b[st][k][4 * tn]);
+                    if (TN == 8)
+                        *reinterpret_cast<float4*>(&b[TN - 4]) =
+                            *reinterpret_cast<const float4*>(&s.b[st][k][BN / 2 + 4 * tn]);
 #pragma unroll
-                for (int i = 0; i < kTM; ++i)
+                    for (int i = 0; i < kTM; ++i)
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
-            }
+                        for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
+                }
+            };
+            if (p.bk == 24) k_loop(std::integral_constant<int, 24>());
+            else if (p.bk == 28) k_loop(std::integral_constant<int, 28>());
+            else k_loop(std::integral_constant<int, 0>());
             mbar_arrive(&s.empty[st]);
             if (++since == p.flush_tiles || it + 1 == my_tiles) {
                 // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
@@ -470,7 +495,42 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         auto part = [&](int i, int j, long long) -> int {
             return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits;
         };
-        if (p.splits == 1) {
+        if (cur.tail_idx >= 0) {
+            // Tail split: every CTA of the tile leaves its partial sums (negative-weight correction
+            // included) in the workspace; the one that arrives last at the tile's counter adds them
+            // up -- in a fixed order, each thread its own 8 x TN outputs -- and applies the epilogue.
+            constexpr int SLOT = kTM * TN * WS_CONS;
+            int* base = p.partials + (long long)cur.tail_idx * p.tail_splits * SLOT;
+            int* mine = base + cur.sp * SLOT;
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                const int col = (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j);
+                const int corr = negc[col] - tailc;
+#pragma unroll
+                for (int i = 0; i < kTM; ++i) __stcg(mine + (i * TN + j) * WS_CONS + t, part(i, j, 0) + corr);
+            }
+            __threadfence();
+            consumer_bar();
+            if (t == 0) {
+                int* cnt = p.counters + cur.tail_idx;
+                const int prev = atomicAdd(cnt, 1);
+                const int lastone = (prev == p.tail_splits - 1);
+                if (lastone) *cnt = 0;  // ready for the next launch
+                s.last_flag = lastone;
+            }
+            consumer_bar();
+            if (s.last_flag) {
+                __threadfence();
+                store_tile<TN, CONV>(
+                    p, cur.m0, cur.n0, tm, tn, BM, BN,
+                    [&](int i, int j, long long) -> int {
+                        int v = 0;
+                        for (int q = 0; q < p.tail_splits; ++q) v += __ldcg(base + q * SLOT + (i * TN + j) * WS_CONS + t);
+                        return v;
+                    },
+                    [&](int) -> int { return 0; });
+            }
+        } else if (p.splits == 1) {
             store_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part,
                                  [&](int col) -> int { return negc[col] - tailc; });
         } else {
@@ -560,13 +620,38 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     if (attr_state < 0) return DS_ERR_UNSUPPORTED;
     const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
     if (gx * gy > 500000000LL) return DS_ERR_RANGE;
-    // Split-K when the output tiles alone fill the SMs badly (few tiles, or a last wave that is
-    // mostly empty) and the caller gave a counter workspace: gridDim.z CTAs share a tile.
     p.splits = 1;
     p.tiles_per_split = p.ntiles;
+    p.tail_items = 0;
+    p.tail_splits = 1;
     const long long tiles = gx * gy;
-    if (p.counters && tiles <= p.counter_slots && p.ntiles >= 16) {
-        const int sms = num_sms();
+    const int sms = num_sms();
+    constexpr long long SLOT_BYTES = (long long)kTM * TN * WS_CONS * 4;
+    if (p.counters && p.partials && p.ntiles >= 12 && tiles % sms != 0) {
+        // Tail split: the tiles beyond the last full wave are cut along K so that the CTAs which
+        // would idle during that wave share its work.  cost = length of the tail in tile times.
+        const long long full = tiles / sms * sms;
+        const int tail = int(tiles - full);
+        double best = 1.0;
+        for (int sp = 2; sp <= 4; ++sp) {
+            if (p.ntiles / sp < 4) break;
+            if ((long long)tail * sp * SLOT_BYTES > p.partial_bytes || tail > p.counter_slots) break;
+            const long long rounds = ((long long)tail * sp + sms - 1) / sms;
+            const double cost = double(rounds) / sp + 0.04;  // + writing and re-reading the partial sums
+            if (cost < best - 0.05) {
+                best = cost;
+                p.tail_splits = sp;
+            }
+        }
+        if (p.tail_splits > 1) {
+            p.tail_items = tail;
+            p.tail_first = int(full);
+            p.tail_tps = (p.ntiles + p.tail_splits - 1) / p.tail_splits;
+            p.tail_splits = (p.ntiles + p.tail_tps - 1) / p.tail_tps;
+        }
+    } else if (p.counters && !p.partials && tiles <= p.counter_slots && p.ntiles >= 16) {
+        // Split-K of every tile through integer atomics on the zeroed output, for callers whose
+        // workspace holds counters only: used when the tiles alone fill the SMs badly.
         auto eff = [&](int sp) {
             const long long ctas = tiles * sp, waves = (ctas + sms - 1) / sms;
             return double(ctas) / double(waves * sms);
@@ -588,8 +673,9 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     }
     p.grid_m = int(gx);
     p.grid_n = int(gy);
-    const long long items = tiles * p.splits;
-    kern<<<dim3((unsigned)(items < num_sms() ? items : num_sms())), WS_NT, smem, st>>>(p);
+    p.full_units = p.tail_items ? p.tail_first : int(tiles * p.splits);
+    const long long items = (long long)p.full_units + (long long)p.tail_items * p.tail_splits;
+    kern<<<dim3((unsigned)(items < sms ? items : sms)), WS_NT, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

@@ -48,15 +48,20 @@ def _no_cpu():
 _WORKSPACES = {}
 
 
+_WS_COUNTERS = 16384                 # int32 arrival counters at the start of the workspace
+_WS_PARTIAL_INTS = 444 * 32768       # partial sums: up to 444 (tile, split) slots of 128 KiB
+
+
 def workspace(device):
-    """Per-device zeroed scratch for split-K arrival counters (see ds_fuse_t.workspace); kernels
-    leave it zero, so one tensor serves every launch on the device's streams in order."""
+    """Per-device scratch for sharing output tiles between CTAs along K (see
+    ds_fuse_t.workspace): zeroed arrival counters followed by room for partial sums.  Kernels
+    leave the counters zero, so one tensor serves every launch on the device's streams in order."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
     ws = _WORKSPACES.get(device)
     if ws is None:
-        ws = _WORKSPACES[device] = torch.zeros(16384, dtype=torch.int32, device=device)
+        ws = _WORKSPACES[device] = torch.zeros(_WS_COUNTERS + _WS_PARTIAL_INTS, dtype=torch.int32, device=device)
     return ws
 
 

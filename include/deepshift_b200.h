@@ -81,11 +81,18 @@ typedef struct {
                                to sums beyond 2^24, so that an int32 tensor handed to the next layer
                                holds exactly the value the reference's fp32 tensor would        */
     int reserved[3];
-    void *workspace;        /* optional scratch for split-K: int32 arrival counters, one per output
-                               tile (256 rows x 128 or 64 columns).  Zero it once; every launch leaves
-                               it zero.  With it, layers whose tiles fill the SMs badly are split
-                               along K (the output is zeroed, partial sums are added with integer
-                               atomics, the last CTA of a tile applies the epilogue).  NULL = never
+    void *workspace;        /* optional scratch for sharing an output tile (256 rows x 128 or 64
+                               columns) between CTAs along K.  The first 16384 int32 are arrival
+                               counters: zero them once; every launch leaves them zero.  Bytes beyond
+                               those 64 KiB (any contents) hold partial sums, 128 KiB per shared tile
+                               and split; about 58 MB serve every layer on a 148-SM GPU.
+                               With counters and partial-sum space, the tiles left over after the last
+                               full wave of CTAs are cut along K into 2-4 ranges so that the SMs
+                               which would idle share them; the CTA that arrives last at a tile's
+                               counter adds the partial sums in a fixed order and applies the
+                               epilogue.  With counters only (<= 64 KiB), layers whose tiles fill the
+                               SMs badly are split along K through integer atomics on the zeroed
+                               output instead.  Results are bit-identical either way.  NULL = never
                                split.  Launches that share a workspace must not overlap on the GPU. */
     long long workspace_bytes;
 } ds_fuse_t;

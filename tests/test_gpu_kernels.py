@@ -306,9 +306,9 @@ def test_no_kernel_wait_ran_out(cuda_device):
 
 @pytest.mark.parametrize("out_f32", [False, True])
 def test_conv_split_k_with_workspace(oracle, cuda_device, out_f32):
-    """Few output tiles and a long K: the launch is split along K (integer atomics into the zeroed
-    output, the last CTA of a tile applies the epilogue).  Same bits as the unsplit result, twice
-    in a row (the arrival counters return to zero)."""
+    """Few output tiles and a long K: the tiles are shared between CTAs along K (partial sums
+    through the workspace, the last CTA of a tile applies the epilogue).  Same bits as the unsplit
+    result, twice in a row (the arrival counters return to zero)."""
     from deepshift_b200 import _ffi, kernels
     rng = np.random.default_rng(21)
     B, C, H, OC = 5, 128, 7, 130
@@ -327,7 +327,26 @@ def test_conv_split_k_with_workspace(oracle, cuda_device, out_f32):
                                    act_integer_bits=I, act_fraction_bits=F, relu=True, residual=_t(res, cuda_device),
                                    round_f32=True)
         assert np.array_equal(out.cpu().numpy(), want)
-    assert int(kernels.workspace(cuda_device).abs().sum()) == 0
+    assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("B", [49, 68])
+def test_conv_tail_wave_is_split(oracle, cuda_device, B):
+    """A few more output tiles than SMs (151 and 209 on 148): the tiles after the last full wave
+    are cut along K, in one and in two rounds of tail units; the other tiles are computed whole
+    by the same launch."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(77 + B)
+    C, H, OC = 32, 28, 100
+    x = acts_q16(rng, (B, C, H, H))
+    shift, sign = weights(rng, (OC, C, 3, 3))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    ref = oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1))
+    for _ in range(2):
+        out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
+                             _cw(shift, sign, cuda_device), 1, 1, act_bits=16)
+        assert np.array_equal(out.cpu().numpy(), ref)
+    assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
 
 
 def test_plain_c_abi_entry_points(oracle, cuda_device):
