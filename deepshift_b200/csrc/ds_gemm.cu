@@ -524,6 +524,9 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.partial_bytes = f.workspace_bytes - (long long)kWorkspaceCounters * 4;
         p.counter_slots = kWorkspaceCounters;
     }
+    p.wd = nullptr;
+    p.negpre = nullptr;
+    p.npad = 0;
     p.full_units = p.tail_first = p.tail_items = 0;
     p.tail_splits = 1;
     p.tail_tps = 0;

@@ -46,6 +46,10 @@ struct GemmParams {
     int tail_tps;        // k-tiles per tail split
     int* partials;       // [tail item][split][kTM * TN][consumer thread]
     long long partial_bytes;
+    // weights expanded once per launch (warp-specialised kernel): +-2^-r as floats, 0 beyond K or N
+    const float* wd;     // [ntiles * bk][npad], null = the producers decode the packed words
+    const int* negpre;   // [ntiles + 1][npad]: negative weights of a column in the k-tiles before t
+    int npad;            // grid_n * BN
     Quant q;
     int rq_lo, rq_hi;
     float inv_scale;  // 2^-F

@@ -87,6 +87,16 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
     return false;
 }
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all()
+{
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 2, %0;" ::"n"(WS_CONS) : "memory"); }
 
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(WS_PROD) : "memory"); }
@@ -129,7 +139,7 @@ __device__ __forceinline__ WsItem ws_item(const GemmParams& p, int unit, int BM,
     return w;
 }
 
-template <int TN, int AM>
+template <int TN, int AM, bool PRE>
 __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 {
     using S = WsSmem<TN>;
@@ -240,13 +250,15 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // the matrix get `padv` (0, or the marker that stands for an unquantised 0 for fp32 kinds).
         auto issue_loads = [&](int tile, int m0) {
             const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
-            const int w0 = tile * p.kt_words;
+            if (!PRE) {
+                const int w0 = tile * p.kt_words;
 #pragma unroll
-            for (int e = 0; e < EW; ++e) {
-                const int jw = (pt + e * WS_PROD) / BN;
-                uint32_t w = 0;
-                if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len) w = uint32_t(__ldg(wrow + w0 + jw));
-                w_reg[e] = w;
+                for (int e = 0; e < EW; ++e) {
+                    const int jw = (pt + e * WS_PROD) / BN;
+                    uint32_t w = 0;
+                    if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len) w = uint32_t(__ldg(wrow + w0 + jw));
+                    w_reg[e] = w;
+                }
             }
             const int tb = tile & 1;
             if (ROW) {
@@ -362,6 +374,17 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             if (negs) atomicAdd(&negc[wn], negs);
         };
 
+        // Expanded weights: rows k0 .. k0+bk-1, BN floats each, straight from global into the stage
+        // (asynchronous 16-byte copies; the x conversion below runs while they are in flight).
+        auto copy_w_async = [&](int tile, int st, int n0) {
+            constexpr int C4 = BN / 4;
+            const float* src = p.wd + (long long)tile * p.bk * p.npad + n0;
+            for (int e = pt; e < p.bk * C4; e += WS_PROD) {
+                const int r = e / C4, c = e - r * C4;
+                cp_async_16(&s.b[st][r][4 * c], src + (long long)r * p.npad + 4 * c);
+            }
+        };
+
         // The CTA walks its items; within an item the k-tiles.  Loads run one k-tile ahead of the
         // stores -- also across item boundaries: while the consumers finish an output tile and run
         // its epilogue, the first k-tiles of the next item are already being staged.
@@ -377,19 +400,25 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 const int st = git % WS_STAGES;
                 if (git >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u)) s.err = 1;
                 const int k0 = tile * p.bk;
-                const bool last = tile + 1 >= p.ntiles;
+                // Expanded weights are 0 beyond K, so the x values stored there need no care.
+                const bool last = !PRE && tile + 1 >= p.ntiles;
+                if (PRE) copy_w_async(tile, st, cur.n0);
                 with_input_kind(p, [&](auto ink_tag) {
                     if (last) store_x(ink_tag, std::true_type(), st, k0);
                     else store_x(ink_tag, std::false_type(), st, k0);
                 });
-                int* negc = s.negc[seq & 3];
-                switch (p.dec.num) {
-                    case 4: store_w(std::integral_constant<int, 4>(), st, negc); break;
-                    case 5: store_w(std::integral_constant<int, 5>(), st, negc); break;
-                    case 6: store_w(std::integral_constant<int, 6>(), st, negc); break;
-                    case 8: store_w(std::integral_constant<int, 8>(), st, negc); break;
-                    case 10: store_w(std::integral_constant<int, 10>(), st, negc); break;
-                    default: store_w(std::integral_constant<int, 16>(), st, negc); break;
+                if (PRE) {
+                    cp_async_wait_all();
+                } else {
+                    int* negc = s.negc[seq & 3];
+                    switch (p.dec.num) {
+                        case 4: store_w(std::integral_constant<int, 4>(), st, negc); break;
+                        case 5: store_w(std::integral_constant<int, 5>(), st, negc); break;
+                        case 6: store_w(std::integral_constant<int, 6>(), st, negc); break;
+                        case 8: store_w(std::integral_constant<int, 8>(), st, negc); break;
+                        case 10: store_w(std::integral_constant<int, 10>(), st, negc); break;
+                        default: store_w(std::integral_constant<int, 16>(), st, negc); break;
+                    }
                 }
                 mbar_arrive(&s.full[st]);
                 ++git;
@@ -443,7 +472,8 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             auto k_loop = [&](auto bk_tag) {
                 constexpr int CBK = decltype(bk_tag)::value;
                 const int nk = CBK ? CBK : p.bk;
-#pragma unroll(CBK ? CBK : 8)
+                constexpr int UNR = CBK ? CBK : 8;
+#pragma unroll(UNR)
                 for (int k = 0; k < nk; ++k) {
                     float a[kTM], b[TN];
                     *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
@@ -489,9 +519,18 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         }
 
         // ---- epilogue of the item ----------------------------------------------------------------
+        // Negative weights of a column inside this unit's K range: counted by the producers while
+        // they decode (tail_neg, the slots past K, belongs to the split that holds the last k-tile),
+        // or read from the prefix counts that come with expanded weights.
         const int* negc = s.negc[seq & 3];
-        // tail_neg belongs to the split that holds the last k-tile
         const int tailc = (cur.t_end == p.ntiles) ? p.tail_neg : 0;
+        auto colcorr = [&](int col) -> int {
+            if (PRE) {
+                const int* np = p.negpre + cur.n0 + col;
+                return __ldg(np + (long long)cur.t_end * p.npad) - __ldg(np + (long long)cur.t_begin * p.npad);
+            }
+            return negc[col] - tailc;
+        };
         auto part = [&](int i, int j, long long) -> int {
             return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits;
         };
@@ -505,7 +544,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
                 const int col = (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j);
-                const int corr = negc[col] - tailc;
+                const int corr = colcorr(col);
 #pragma unroll
                 for (int i = 0; i < kTM; ++i) __stcg(mine + (i * TN + j) * WS_CONS + t, part(i, j, 0) + corr);
             }
@@ -531,13 +570,11 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     [&](int) -> int { return 0; });
             }
         } else if (p.splits == 1) {
-            store_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part,
-                                 [&](int col) -> int { return negc[col] - tailc; });
+            store_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part, colcorr);
         } else {
             // split-K: add the partial sums into the zeroed output; the CTA that arrives last at
             // this tile's counter reads the totals back and applies the epilogue in place.
-            reduce_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part,
-                                  [&](int col) -> int { return negc[col] - tailc; });
+            reduce_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part, colcorr);
             __threadfence();
             consumer_bar();
             if (t == 0) {
@@ -558,10 +595,68 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         }
         // All consumers have read this item's negative-weight counts before they are cleared for
         // a later item (the producers are filling other sets meanwhile).
-        consumer_bar();
-        for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
+        if (!PRE) {
+            consumer_bar();
+            for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
+        }
     }
     if (bad) g_ws_error = 1;
+}
+
+// Expands the packed weights of one launch into floats laid out as the k-tiles want them:
+// wd[t * bk + j][n] = +-2^-r, 0 for a zero weight and for every slot beyond K or N, and counts the
+// negative ones per (k-tile, column).  One thread per (column, k-tile), columns fastest.
+__global__ void __launch_bounds__(256) expand_weights_kernel(const GemmParams p, float* wd, int* negcnt)
+{
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)p.npad * p.ntiles) return;
+    const int t = int(idx / p.npad), n = int(idx - (long long)t * p.npad);
+    const uint32_t fmask = (1u << p.dec.fw) - 1u;
+    float* dst = wd + (long long)t * p.bk * p.npad + n;
+    int negs = 0;
+    for (int jw = 0; jw < p.kt_words; ++jw) {
+        const int word = t * p.kt_words + jw;
+        uint32_t w = 0;
+        const bool have = n < p.N && word < p.dec.row_len;
+        if (have) w = uint32_t(__ldg(p.packed + (long long)n * p.dec.row_len + word));
+        for (int i = 0; i < p.dec.num; ++i) {
+            const int k = word * p.dec.num + i;
+            int neg;
+            const float v = decode_f32(w & fmask, p.dec, have && k < p.K, neg);
+            w >>= p.dec.fw;
+            dst[(long long)(jw * p.dec.num + i) * p.npad] = v;
+            negs += neg;
+        }
+    }
+    negcnt[idx] = negs;
+}
+
+// Exclusive prefix sums of the per-tile counts along the k-tiles: row t of `negpre` becomes the
+// number of negative weights of the column in tiles 0 .. t-1, row ntiles the total.  A block
+// takes 32 columns; its 32 warps each sum one segment of the tiles, exchange the segment sums
+// through shared memory and then write the prefixes of their segment.
+__global__ void __launch_bounds__(1024) negative_prefix_kernel(const int* __restrict__ negcnt, int* __restrict__ negpre,
+                                                               int ntiles, int npad)
+{
+    __shared__ int seg[32][33];
+    const int lane = threadIdx.x, sg = threadIdx.y;
+    const int n = blockIdx.x * 32 + lane;
+    const bool live = n < npad;
+    const int per = (ntiles + 31) / 32;
+    const int t0 = min(ntiles, sg * per), t1 = min(ntiles, t0 + per);
+    int sum = 0;
+    if (live)
+        for (int t = t0; t < t1; ++t) sum += negcnt[(long long)t * npad + n];
+    seg[sg][lane] = sum;
+    __syncthreads();
+    int run = 0;
+    for (int q = 0; q < sg; ++q) run += seg[q][lane];
+    if (!live) return;
+    for (int t = t0; t < t1; ++t) {
+        negpre[(long long)t * npad + n] = run;
+        run += negcnt[(long long)t * npad + n];
+    }
+    if (sg == 31) negpre[(long long)ntiles * npad + n] = run;
 }
 
 // Chooses the k-tile: a multiple of num (whole packed words) and of the staging granularity
@@ -598,18 +693,17 @@ int num_sms()
     return sms;
 }
 
-template <int TN, int AM>
-int ws_launch_cfg(GemmParams p, cudaStream_t st)
+// Sets the shared-memory attribute of one kernel instantiation once and checks that it can be used.
+template <int TN, int AM, bool PRE>
+int ws_kernel_ready()
 {
-    using S = WsSmem<TN>;
-    if (!ws_choose_tile<AM>(p)) return DS_ERR_UNSUPPORTED;
-    auto kern = ws_kernel<TN, AM>;
-    const size_t smem = sizeof(S);
     static int attr_state = 0;  // per instantiation: 0 unknown, 1 usable, -1 not usable
     if (attr_state == 0) {
+        auto kern = ws_kernel<TN, AM, PRE>;
         cudaFuncAttributes fa;
         if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(WsSmem<TN>))) !=
+                cudaSuccess) {
             cudaGetLastError();
             return DS_ERR_CUDA;
         }
@@ -617,7 +711,16 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
         // other one the consumers could wait for registers for ever, so the kernel is not used.
         attr_state = (fa.numRegs == WS_LAUNCH_REGS) ? 1 : -1;
     }
-    if (attr_state < 0) return DS_ERR_UNSUPPORTED;
+    return attr_state < 0 ? DS_ERR_UNSUPPORTED : DS_OK;
+}
+
+template <int TN, int AM>
+int ws_launch_cfg(GemmParams p, cudaStream_t st)
+{
+    using S = WsSmem<TN>;
+    if (!ws_choose_tile<AM>(p)) return DS_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(S);
+    if (int rc = ws_kernel_ready<TN, AM, false>()) return rc;
     const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
     if (gx * gy > 500000000LL) return DS_ERR_RANGE;
     p.splits = 1;
@@ -627,6 +730,29 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     const long long tiles = gx * gy;
     const int sms = num_sms();
     constexpr long long SLOT_BYTES = (long long)kTM * TN * WS_CONS * 4;
+    // Expanded weights: when many row tiles would each decode the same packed words again, decode
+    // them once per launch into the front of the workspace (two small kernels ahead of this one).
+    p.npad = int(gy) * S::BN;
+    bool pre = false;
+    if (p.partials && gx >= 8) {
+        const long long wd_floats = (long long)p.ntiles * p.bk * p.npad;
+        const long long neg_ints = (long long)(p.ntiles + 1) * p.npad, cnt_ints = (long long)p.ntiles * p.npad;
+        const long long need = ((wd_floats + neg_ints + cnt_ints) * 4 + 255) / 256 * 256;
+        if (need <= p.partial_bytes && ws_kernel_ready<TN, AM, true>() == DS_OK) {
+            float* wd = reinterpret_cast<float*>(p.partials);
+            int* negpre = p.partials + wd_floats;
+            p.partials += need / 4;
+            p.partial_bytes -= need;
+            p.wd = wd;
+            p.negpre = negpre;
+            const long long threads = (long long)p.npad * p.ntiles;
+            int* negcnt = negpre + neg_ints;
+            expand_weights_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(p, wd, negcnt);
+            negative_prefix_kernel<<<(p.npad + 31) / 32, dim3(32, 32), 0, st>>>(negcnt, negpre, p.ntiles, p.npad);
+            if (cudaGetLastError() != cudaSuccess) return DS_ERR_CUDA;
+            pre = true;
+        }
+    }
     if (p.counters && p.partials && p.ntiles >= 12 && tiles % sms != 0) {
         // Tail split: the tiles beyond the last full wave are cut along K so that the CTAs which
         // would idle during that wave share its work.  cost = length of the tail in tile times.
@@ -675,7 +801,9 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     p.grid_n = int(gy);
     p.full_units = p.tail_items ? p.tail_first : int(tiles * p.splits);
     const long long items = (long long)p.full_units + (long long)p.tail_items * p.tail_splits;
-    kern<<<dim3((unsigned)(items < sms ? items : sms)), WS_NT, smem, st>>>(p);
+    const dim3 grid((unsigned)(items < sms ? items : sms));
+    if (pre) ws_kernel<TN, AM, true><<<grid, WS_NT, smem, st>>>(p);
+    else ws_kernel<TN, AM, false><<<grid, WS_NT, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

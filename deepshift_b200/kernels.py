@@ -49,7 +49,8 @@ _WORKSPACES = {}
 
 
 _WS_COUNTERS = 16384                 # int32 arrival counters at the start of the workspace
-_WS_PARTIAL_INTS = 444 * 32768       # partial sums: up to 444 (tile, split) slots of 128 KiB
+_WS_PARTIAL_INTS = 444 * 32768 + (8 << 20)  # expanded weights of one layer (32 MiB) and partial sums:
+                                             # up to 444 (tile, split) slots of 128 KiB
 
 
 def workspace(device):

@@ -84,8 +84,11 @@ typedef struct {
     void *workspace;        /* optional scratch for sharing an output tile (256 rows x 128 or 64
                                columns) between CTAs along K.  The first 16384 int32 are arrival
                                counters: zero them once; every launch leaves them zero.  Bytes beyond
-                               those 64 KiB (any contents) hold partial sums, 128 KiB per shared tile
-                               and split; about 58 MB serve every layer on a 148-SM GPU.
+                               those 64 KiB (any contents) hold, per launch, the layer's weights
+                               expanded to fp32 (4 bytes per weight, when the launch has at least 8
+                               row tiles) and partial sums, 128 KiB per shared tile and split; about
+                               90 MB serve every ResNet-18 layer on a 148-SM GPU, less is used as far
+                               as it goes.
                                With counters and partial-sum space, the tiles left over after the last
                                full wave of CTAs are cut along K into 2-4 ranges so that the SMs
                                which would idle share them; the CTA that arrives last at a tile's
