@@ -4,6 +4,7 @@
 The file is git-ignored but travels with the source tree, so a machine without nvcc can use
 a library built elsewhere from the same sources.
 """
+import concurrent.futures
 import glob
 import hashlib
 import os
@@ -52,20 +53,44 @@ def nvcc_path():
 
 
 def build(force=False, verbose=False, extra_flags=()):
-    """Compile the library if the sources changed.  Returns the library path."""
+    """Compile the library if the sources changed.  Returns the library path.
+
+    Every ``.cu`` file is compiled to an object file by its own nvcc process (they run side by
+    side), then the objects are linked into the shared library."""
     if not force and is_current():
         return LIB_PATH
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found and %s is missing or stale" % LIB_PATH)
     os.makedirs(LIB_DIR, exist_ok=True)
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
     env = dict(os.environ)
     env.pop("CC", None)
     env.pop("CXX", None)
-    cmd = [nvcc] + NVCC_FLAGS + list(extra_flags) + ["-ccbin", "g++", "-o", LIB_PATH] + _sources()
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"] + list(extra_flags) + ["-ccbin", "g++"]
+
+    def compile_one(src):
+        obj = os.path.join(obj_dir, os.path.splitext(os.path.basename(src))[0] + ".o")
+        cmd = [nvcc] + compile_flags + ["-c", "-o", obj, src]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        return obj, res.returncode, res.stdout
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(8, os.cpu_count() or 1))) as pool:
+        results = list(pool.map(compile_one, _sources()))
+    for _, rc, out in results:
+        if verbose or rc:
+            print(out, end="")
+    bad = [obj for obj, rc, _ in results if rc]
+    if bad:
+        raise RuntimeError("nvcc failed for: " + ", ".join(os.path.basename(b) for b in bad))
+    cmd = [nvcc, "-shared", "-ccbin", "g++", "-o", LIB_PATH] + [obj for obj, _, _ in results]
     if verbose:
-        print(" ".join(cmd))
+        print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True, env=env)
+    shutil.rmtree(obj_dir, ignore_errors=True)
     with open(STAMP, "w") as fh:
         fh.write(_digest())
     return LIB_PATH

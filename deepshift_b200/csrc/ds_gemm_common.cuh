@@ -50,6 +50,7 @@ struct GemmParams {
     const float* wd;     // [ntiles * bk][npad], null = the producers decode the packed words
     const int* negpre;   // [ntiles + 1][npad]: negative weights of a column in the k-tiles before t
     int npad;            // grid_n * BN
+    int* err_flag;       // set to 1 by a kernel whose bounded wait ran out
     Quant q;
     int rq_lo, rq_hi;
     float inv_scale;  // 2^-F
@@ -253,9 +254,15 @@ __device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
 // K with integer atomics when no epilogue is fused.
 int launch_small_linear(const GemmParams& p, cudaStream_t st);
 
-// Warp-specialised FP32-pipe kernel (ds_gemm_ws.cu).  am: AM_LINEAR, AM_TABLE or the window
-// width of the row mode.  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller then
-// falls back to the table mode or the integer path.
+// Warp-specialised FP32-pipe convolution kernel (ds_gemm_ws.cuh).  am: AM_TABLE or the window
+// width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
+// then falls back to the table mode or the integer path.  The per-width entry points are what
+// launch_ws dispatches to; they expect GemmParams::err_flag to be set.
 int launch_ws(const GemmParams& p, int am, cudaStream_t st);
+int launch_ws_am1(const GemmParams& p, cudaStream_t st);
+int launch_ws_am3(const GemmParams& p, cudaStream_t st);
+int launch_ws_am5(const GemmParams& p, cudaStream_t st);
+int launch_ws_am7(const GemmParams& p, cudaStream_t st);
+int launch_ws_table(const GemmParams& p, cudaStream_t st);
 
 }  // namespace ds

@@ -1,830 +1,38 @@
-// Warp-specialised FP32-pipe shift "GEMM" / convolution for sm_100a.
-//
-// Arithmetic: see ds_gemm.cu (one FFMA with round-toward-minus-infinity per term, magic-offset
-// accumulators drained into shared int32 slots).  This file changes how the work is divided:
-//
-//   * 16 consumer warps (512 threads) own a 256 x BN output tile, 8 x TN outputs per thread.
-//     Their loop is nothing but shared-memory fragment loads and FFMAs; they never touch
-//     global memory before the epilogue and never wait on another consumer warp.
-//   * 8 producer warps (256 threads) gather x (implicit im2col, zero padding by predication,
-//     int32 -> x + 0.5 conversion or the fused fp32 quantiser), fetch the packed weight words
-//     and decode them through the lookup table, one k-tile ahead of the consumers.
-//   * The two groups meet only at mbarriers: full[s] (256 producer arrivals) and empty[s] (512
-//     consumer arrivals) for each of the two stages.  Global-load latency, the decode chains
-//     and the stores of a stage all overlap the FFMA stream of the previous stage, so the
-//     FMA pipe no longer idles while "everybody stages".
-//
-// Every wait is bounded: a wait that runs out records an error and lets the thread continue,
-// so the kernel always terminates; the host can read the flag with ds_last_kernel_error().
+// Dispatcher of the warp-specialised kernel (ds_gemm_ws.cuh).  The instantiations live in one
+// translation unit per window width (ds_ws_am*.cu) so that they compile side by side; this file
+// owns what they share: the flag that a kernel sets when one of its bounded waits ran out.
 #include "ds_gemm_common.cuh"
 
 namespace ds {
 namespace {
 
-constexpr int WS_CONS = 512;   // consumer threads
-constexpr int WS_PROD = 256;   // producer threads
-constexpr int WS_NT = WS_CONS + WS_PROD;
-constexpr int WS_BM = 256;     // rows of x per CTA
-constexpr int WS_BKT = 28;     // largest k-tile
-constexpr int WS_STAGES = 2;
-// Register split after the roles part.  The CTA starts with 768 * 80 registers; what the
-// producers give back (256 * (80 - 56) = 6144) is all the consumers can take (512 * (88 - 80) =
-// 4096): a larger request would wait for registers that never come.
-constexpr int WS_LAUNCH_REGS = 80, WS_PROD_REGS = 56, WS_CONS_REGS = 88;
-static_assert(WS_CONS * (WS_CONS_REGS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - WS_PROD_REGS), "register pool");
-constexpr int WS_WAIT_LIMIT = 1 << 12;  // rounds of one mbarrier wait before giving up
-constexpr unsigned WS_WAIT_NS = 1000000;  // suspend-time hint of one round, nanoseconds
+__device__ int g_ws_error = 0;  // never set in a correct run
 
-__device__ int g_ws_error = 0;  // set when a bounded wait ran out (never in a correct run)
-
-template <int TN>
-struct WsSmem {
-    static constexpr int BN = 16 * TN;
-    static constexpr int AP = WS_BM + 4;
-    alignas(16) float a[WS_STAGES][WS_BKT][AP];  // x + 0.5
-    alignas(16) float b[WS_STAGES][WS_BKT][BN];  // +-2^-r
-    alignas(16) KEntry ktab[WS_STAGES][WS_BKT];
-    alignas(8) unsigned long long full[WS_STAGES];
-    alignas(8) unsigned long long empty[WS_STAGES];
-    int lut0[256];  // float bits of the decoded weight per field value
-    // Negative weights per output column.  Four sets, used round-robin by item: the producers can
-    // be two items ahead of the consumers (items of a single k-tile), and a set is cleared by the
-    // consumers only after their epilogue.
-    int negc[4][BN];
-    int err;
-    int last_flag;  // split-K: this CTA arrived last at its tile's counter
-    int accs[kTM * TN * WS_CONS];  // drained accumulators, [slot][consumer thread]
-};
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
-{
-    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// Bounded wait for the phase with the given parity to complete.  Each try_wait lets the hardware
-// suspend the thread for up to WS_WAIT_NS before it reports "not yet", so a waiting warp issues
-// almost nothing.  Returns false after WS_WAIT_LIMIT such rounds (seconds; a correct run waits
-// microseconds).
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity)
-{
-    const unsigned addr = smem_u32(bar);
-    for (int i = 0; i < WS_WAIT_LIMIT; ++i) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity), "r"(WS_WAIT_NS)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-
-__device__ __forceinline__ void cp_async_wait_all()
-{
-    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-}
-
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 2, %0;" ::"n"(WS_CONS) : "memory"); }
-
-__device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(WS_PROD) : "memory"); }
-
-// ---------------------------------------------------------------------------------------------
-// Work unit = (output tile, K range).  Units are numbered with the row tile fastest, so CTAs that
-// run side by side share weight tiles in L2.  Units [0, full_units) cover every output tile
-// `splits` times (1 = each tile whole); the units after them are the tail: the last tail_items
-// tiles, each cut into tail_splits K ranges so that the last wave of CTAs is short instead of
-// mostly empty.
-struct WsItem {
-    int m0, n0, t_begin, t_end, tile_id;
-    int tail_idx;  // >= 0: tail unit of that tail tile, partial sums go through the workspace
-    int sp;
-};
-
-__device__ __forceinline__ WsItem ws_item(const GemmParams& p, int unit, int BM, int BN)
-{
-    WsItem w;
-    int tile, tps;
-    if (unit < p.full_units) {
-        const int tiles = p.grid_m * p.grid_n;
-        w.sp = unit / tiles;
-        tile = unit - w.sp * tiles;
-        tps = p.tiles_per_split;
-        w.tail_idx = -1;
-    } else {
-        const int v = unit - p.full_units;
-        w.sp = v / p.tail_items;
-        w.tail_idx = v - w.sp * p.tail_items;
-        tile = p.tail_first + w.tail_idx;
-        tps = p.tail_tps;
-    }
-    const int nt = tile / p.grid_m, mt = tile - nt * p.grid_m;
-    w.m0 = mt * BM;
-    w.n0 = nt * BN;
-    w.t_begin = w.sp * tps;
-    w.t_end = min(p.ntiles, w.t_begin + tps);
-    w.tile_id = tile;
-    return w;
-}
-
-template <int TN, int AM, bool PRE>
-__global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
-{
-    using S = WsSmem<TN>;
-    constexpr bool CONV = AM != AM_LINEAR;
-    constexpr bool ROW = AM >= 1;
-    constexpr int KW = ROW ? AM : 1;
-    constexpr int BM = WS_BM, BN = S::BN;
-    constexpr int TMG = 32, TNG = 16;
-    static_assert(offsetof(S, b) % 16 == 0 && offsetof(S, ktab) % 16 == 0 && offsetof(S, full) % 8 == 0, "alignment");
-
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    S& s = *reinterpret_cast<S*>(smem_raw);
-
-    const int t = threadIdx.x;
-    const int total_items = p.full_units + p.tail_items * p.tail_splits;
-
-    // ---- set-up by all threads ------------------------------------------------------------------
-    for (int f = t; f < (1 << p.dec.fw); f += WS_NT) {
-        int neg;
-        s.lut0[f] = __float_as_int(decode_f32(uint32_t(f), p.dec, true, neg));
-    }
-    for (int i = t; i < 4 * BN; i += WS_NT) (&s.negc[0][0])[i] = 0;
-    if (t == 0) {
-        for (int i = 0; i < WS_STAGES; ++i) {
-            mbar_init(&s.full[i], WS_PROD);
-            mbar_init(&s.empty[i], WS_CONS);
-        }
-        s.err = 0;
-    }
-    __syncthreads();
-
-    if (t >= WS_CONS) {
-        // =========================== producers ==================================================
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_PROD_REGS));
-        const int pt = t - WS_CONS;
-        constexpr int PIX = BM / WS_PROD;  // rows of the x tile per producer thread (conv)
-        const char* x_pix[PIX];
-        uint32_t rowmask[PIX], colmask[PIX];
-        // weight words: column n = wi % BN, word jw = wi / BN of the k-tile, wi = pt + WS_PROD * e
-        constexpr int EW = (BN * (WS_BKT / 4) + WS_PROD - 1) / WS_PROD;
-        const int wn = pt & (BN - 1);
-        const int32_t* wrow = nullptr;
-        const uint32_t fmask = (1u << p.dec.fw) - 1u;
-
-        // Registers that hold one k-tile of this thread's x values and weight words between the
-        // global loads (issued one tile ahead) and their conversion into shared memory.
-        constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows of the largest k-tile, row mode
-        constexpr int XN = ROW ? RMAX * KW : WS_BKT;      // x values per thread per tile (conv)
-        constexpr int LIN_RP = WS_PROD / 32;              // linear: x rows per pass
-        constexpr int LIN_N = BM / LIN_RP;                // linear: x values per thread per tile
-        constexpr int XREG = CONV ? XN * PIX : LIN_N;
-        int xr[XREG];
-        uint32_t w_reg[EW];
-        static_assert(XREG <= 32, "producer registers");
-
-        // Per-item state of this thread: the x rows it gathers and the weight row it decodes.
-        auto setup_item = [&](const WsItem& w) {
-            wrow = (w.n0 + wn < p.N) ? p.packed + (long long)(w.n0 + wn) * p.dec.row_len : nullptr;
-            if (CONV) {
-#pragma unroll
-                for (int q = 0; q < PIX; ++q) {
-                    const int m = w.m0 + pt + q * WS_PROD;
-                    x_pix[q] = reinterpret_cast<const char*>(p.x);
-                    rowmask[q] = colmask[q] = 0;
-                    if (m < p.M) {
-                        const int b = m / p.P, pp = m - b * p.P;
-                        const int oh = pp / p.OW, ow = pp - oh * p.OW;
-                        const int ih0 = oh * p.sh - p.ph, iw0 = ow * p.sw - p.pw;
-                        for (int kh = 0; kh < p.KH; ++kh)
-                            if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[q] |= 1u << kh;
-                        for (int kw = 0; kw < p.KW; ++kw)
-                            if (unsigned(iw0 + kw) < unsigned(p.W)) colmask[q] |= 1u << kw;
-                        // address of (b, 0, ih0, iw0): may lie outside the tensor, only valid taps are read
-                        x_pix[q] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4;
-                    }
-                }
-            }
-        };
-
-        auto fill_table = [&](int tile) {
-            if (!CONV || pt >= WS_BKT) return;
-            KEntry e;
-            e.pad = 0;
-            e.off = 0;
-            e.kh = 31;
-            e.kw = 0;
-            if (ROW) {
-                const int row = tile * p.rows_per_tile + pt;  // global (ic,kh) row index
-                if (pt < p.rows_per_tile && row < p.C * p.KH) {
-                    const int ic = magic_div(row, p.magic_kh);
-                    e.kh = row - ic * p.KH;
-                    e.off = (ic * p.H * p.W + e.kh * p.W) * 4;
-                }
-            } else {
-                const int k = tile * p.bk + pt;
-                if (pt < p.bk && k < p.K) {
-                    const int ic = magic_div(k, p.magic_khw);
-                    const int tap = k - ic * (p.KH * p.KW);
-                    e.kh = magic_div(tap, p.magic_kw);
-                    e.kw = tap - e.kh * p.KW;
-                    e.off = (ic * p.H * p.W + e.kh * p.W + e.kw) * 4;
-                }
-            }
-            s.ktab[tile & 1][pt] = e;
-        };
-
-        // Issues the global loads of one k-tile into registers.  Positions outside the image or
-        // the matrix get `padv` (0, or the marker that stands for an unquantised 0 for fp32 kinds).
-        auto issue_loads = [&](int tile, int m0) {
-            const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
-            if (!PRE) {
-                const int w0 = tile * p.kt_words;
-#pragma unroll
-                for (int e = 0; e < EW; ++e) {
-                    const int jw = (pt + e * WS_PROD) / BN;
-                    uint32_t w = 0;
-                    if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len) w = uint32_t(__ldg(wrow + w0 + jw));
-                    w_reg[e] = w;
-                }
-            }
-            const int tb = tile & 1;
-            if (ROW) {
-#pragma unroll
-                for (int u = 0; u < RMAX; ++u) {
-                    const int2 e = *reinterpret_cast<const int2*>(&s.ktab[tb][u]);  // rows past the tile: kh = 31
-#pragma unroll
-                    for (int q = 0; q < PIX; ++q) {
-                        const bool rv = (rowmask[q] >> e.y) & 1u;
-                        const int* rowp = reinterpret_cast<const int*>(x_pix[q] + e.x);
-#pragma unroll
-                        for (int kw = 0; kw < KW; ++kw) {
-                            int val = padv;
-                            if (rv && (colmask[q] & (1u << kw))) val = __ldg(rowp + kw);
-                            xr[(q * RMAX + u) * KW + kw] = val;
-                        }
-                    }
-                }
-            } else if (CONV) {
-#pragma unroll
-                for (int u = 0; u < WS_BKT; ++u) {
-                    const int4 e = *reinterpret_cast<const int4*>(&s.ktab[tb][u]);
-#pragma unroll
-                    for (int q = 0; q < PIX; ++q) {
-                        int val = padv;
-                        if (((rowmask[q] >> e.y) & (colmask[q] >> e.z) & 1u) != 0u)
-                            val = __ldg(reinterpret_cast<const int*>(x_pix[q] + e.x));
-                        xr[q * WS_BKT + u] = val;
-                    }
-                }
-            } else {
-                // x is [M,K]: lanes run along k (32 wide), LIN_RP rows per pass
-                const int kl = pt & 31;
-                const int k = tile * p.bk + kl;
-                const bool kval = kl < p.bk && k < p.K;
-#pragma unroll
-                for (int u = 0; u < LIN_N; ++u) {
-                    const int ml = LIN_RP * u + (pt >> 5);
-                    int val = padv;
-                    if (kval && m0 + ml < p.M)
-                        val = __ldg(static_cast<const int32_t*>(p.x) + ((long long)(m0 + ml) * p.K + k));
-                    xr[u] = val;
-                }
-            }
-        };
-
-        // Converts the registers of one k-tile and stores them into stage `st`.  INK: input kind;
-        // LAST: the tile may reach past K, where x is stored as 0 (see the weight tail below).
-        auto store_x = [&](auto ink_tag, auto last_tag, int st, int k0) {
-            constexpr int INK = decltype(ink_tag)::value;
-            constexpr bool LAST = decltype(last_tag)::value;
-            if (ROW) {
-#pragma unroll
-                for (int u = 0; u < RMAX; ++u) {
-                    if (u < p.rows_per_tile) {
-#pragma unroll
-                        for (int q = 0; q < PIX; ++q)
-#pragma unroll
-                            for (int kw = 0; kw < KW; ++kw) {
-                                float o = operand_of<true, INK>(p, xr[(q * RMAX + u) * KW + kw]);
-                                if (LAST && k0 + u * KW + kw >= p.K) o = 0.f;
-                                s.a[st][u * KW + kw][pt + q * WS_PROD] = o;
-                            }
-                    }
-                }
-            } else if (CONV) {
-#pragma unroll
-                for (int u = 0; u < WS_BKT; ++u) {
-                    if (u < p.bk) {
-#pragma unroll
-                        for (int q = 0; q < PIX; ++q) {
-                            float o = operand_of<true, INK>(p, xr[q * WS_BKT + u]);
-                            if (LAST && k0 + u >= p.K) o = 0.f;
-                            s.a[st][u][pt + q * WS_PROD] = o;
-                        }
-                    }
-                }
-            } else {
-                const int kl = pt & 31;
-                if (kl < WS_BKT) {
-#pragma unroll
-                    for (int u = 0; u < LIN_N; ++u) {
-                        float o = operand_of<true, INK>(p, xr[u]);
-                        if (LAST && k0 + kl >= p.K) o = 0.f;
-                        s.a[st][kl][LIN_RP * u + (pt >> 5)] = o;
-                    }
-                }
-            }
-        };
-
-        // Decodes this thread's weight words through the table into stage `st`.  Slots k >= K of
-        // the last words decode like any field (a zero field is -2^0); the x values stored there
-        // are 0, so they add nothing, and the epilogue takes their share (tail_neg) out of the
-        // negative-weight count `negc` of the item.
-        auto store_w = [&](auto num_tag, int st, int* negc) {
-            constexpr int NUM = decltype(num_tag)::value;
-            int negs = 0;
-#pragma unroll
-            for (int e = 0; e < EW; ++e) {
-                const int jw = (pt + e * WS_PROD) / BN;
-                if (jw < p.kt_words) {
-                    uint32_t w = w_reg[e];
-                    float* dst = &s.b[st][jw * NUM][wn];
-#pragma unroll
-                    for (int i = 0; i < NUM; ++i) {
-                        const int v0 = s.lut0[w & fmask];
-                        w >>= p.dec.fw;
-                        dst[i * BN] = __int_as_float(v0);
-                        negs += int(uint32_t(v0) >> 31);
-                    }
-                }
-            }
-            if (negs) atomicAdd(&negc[wn], negs);
-        };
-
-        // Expanded weights: rows k0 .. k0+bk-1, BN floats each, straight from global into the stage
-        // (asynchronous 16-byte copies; the x conversion below runs while they are in flight).
-        auto copy_w_async = [&](int tile, int st, int n0) {
-            constexpr int C4 = BN / 4;
-            const float* src = p.wd + (long long)tile * p.bk * p.npad + n0;
-            for (int e = pt; e < p.bk * C4; e += WS_PROD) {
-                const int r = e / C4, c = e - r * C4;
-                cp_async_16(&s.b[st][r][4 * c], src + (long long)r * p.npad + 4 * c);
-            }
-        };
-
-        // The CTA walks its items; within an item the k-tiles.  Loads run one k-tile ahead of the
-        // stores -- also across item boundaries: while the consumers finish an output tile and run
-        // its epilogue, the first k-tiles of the next item are already being staged.
-        int item = blockIdx.x, seq = 0, git = 0;
-        if (item < total_items) {
-            WsItem cur = ws_item(p, item, BM, BN);
-            int tile = cur.t_begin;
-            setup_item(cur);
-            fill_table(tile);
-            if (CONV) producer_bar();
-            issue_loads(tile, cur.m0);
-            while (true) {
-                const int st = git % WS_STAGES;
-                if (git >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u)) s.err = 1;
-                const int k0 = tile * p.bk;
-                // Expanded weights are 0 beyond K, so the x values stored there need no care.
-                const bool last = !PRE && tile + 1 >= p.ntiles;
-                if (PRE) copy_w_async(tile, st, cur.n0);
-                with_input_kind(p, [&](auto ink_tag) {
-                    if (last) store_x(ink_tag, std::true_type(), st, k0);
-                    else store_x(ink_tag, std::false_type(), st, k0);
-                });
-                if (PRE) {
-                    cp_async_wait_all();
-                } else {
-                    int* negc = s.negc[seq & 3];
-                    switch (p.dec.num) {
-                        case 4: store_w(std::integral_constant<int, 4>(), st, negc); break;
-                        case 5: store_w(std::integral_constant<int, 5>(), st, negc); break;
-                        case 6: store_w(std::integral_constant<int, 6>(), st, negc); break;
-                        case 8: store_w(std::integral_constant<int, 8>(), st, negc); break;
-                        case 10: store_w(std::integral_constant<int, 10>(), st, negc); break;
-                        default: store_w(std::integral_constant<int, 16>(), st, negc); break;
-                    }
-                }
-                mbar_arrive(&s.full[st]);
-                ++git;
-                // next (item, k-tile)
-                if (++tile >= cur.t_end) {
-                    item += gridDim.x;
-                    if (item >= total_items) break;
-                    ++seq;
-                    cur = ws_item(p, item, BM, BN);
-                    tile = cur.t_begin;
-                    setup_item(cur);
-                }
-                fill_table(tile);
-                if (CONV) producer_bar();
-                issue_loads(tile, cur.m0);
-            }
-        }
-        if (s.err) g_ws_error = 1;
-        return;
-    }
-
-    // =============================== consumers ====================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_CONS_REGS));
-    // A warp covers 8 x 4 thread tiles, 8 along the direction in which the output is contiguous.
-    const int lane = t & 31, warp = t >> 5;
-    int tm, tn;
-    if (CONV) {
-        constexpr int WMG = TMG / 8;
-        tm = (warp % WMG) * 8 + (lane & 7);
-        tn = (warp / WMG) * 4 + (lane >> 3);
-    } else {
-        constexpr int WNG = TNG / 8;
-        tn = (warp % WNG) * 8 + (lane & 7);
-        tm = (warp / WNG) * 4 + (lane >> 3);
-    }
-    float accf[kTM][TN];
-    bool bad = false;
-    int git = 0, seq = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++seq) {
-        const WsItem cur = ws_item(p, item, BM, BN);
-        const int my_tiles = cur.t_end - cur.t_begin;
-#pragma unroll
-        for (int i = 0; i < kTM; ++i)
-#pragma unroll
-            for (int j = 0; j < TN; ++j) accf[i][j] = kMagic;
-        int ndrains = 0, since = 0;
-        for (int it = 0; it < my_tiles; ++it, ++git) {
-            const int st = git % WS_STAGES;
-            if (!mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u)) bad = true;
-            // The k-tile sizes of 3x3, 1x1 / 7x7 and 5x5 windows get fully unrolled loops.
-            auto k_loop = [&](auto bk_tag) {
-                constexpr int CBK = decltype(bk_tag)::value;
-                const int nk = CBK ? CBK : p.bk;
-                constexpr int UNR = CBK ? CBK : 8;
-#pragma unroll(UNR)
-                for (int k = 0; k < nk; ++k) {
-                    float a[kTM], b[TN];
-                    *reinterpret_cast<float4*>(&a[0]) = *reinterpret_cast<const float4*>(&s.a[st][k][4 * tm]);
-                    *reinterpret_cast<float4*>(&a[4]) = *reinterpret_cast<const float4*>(&s.a[st][k][BM / 2 + 4 * tm]);
-                    *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(&s.b[st][k][4 * tn]);
-                    if (TN == 8)
-                        *reinterpret_cast<float4*>(&b[TN - 4]) =
-                            *reinterpret_cast<const float4*>(&s.b[st][k][BN / 2 + 4 * tn]);
-#pragma unroll
-                    for (int i = 0; i < kTM; ++i)
-#pragma unroll
-                        for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a[i], b[j], accf[i][j]);
-                }
-            };
-            if (p.bk == 24) k_loop(std::integral_constant<int, 24>());
-            else if (p.bk == 28) k_loop(std::integral_constant<int, 28>());
-            else k_loop(std::integral_constant<int, 0>());
-            mbar_arrive(&s.empty[st]);
-            if (++since == p.flush_tiles || it + 1 == my_tiles) {
-                // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
-                // slots and restart them; the epilogue removes ndrains * kMagicBits.  The first
-                // drain of an item overwrites what the previous item left in the slots.
-                if (ndrains == 0) {
-#pragma unroll
-                    for (int i = 0; i < kTM; ++i)
-#pragma unroll
-                        for (int j = 0; j < TN; ++j) {
-                            s.accs[(i * TN + j) * WS_CONS + t] = __float_as_int(accf[i][j]);
-                            accf[i][j] = kMagic;
-                        }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < kTM; ++i)
-#pragma unroll
-                        for (int j = 0; j < TN; ++j) {
-                            red_shared_add(&s.accs[(i * TN + j) * WS_CONS + t], __float_as_int(accf[i][j]));
-                            accf[i][j] = kMagic;
-                        }
-                }
-                ++ndrains;
-                since = 0;
-            }
-        }
-
-        // ---- epilogue of the item ----------------------------------------------------------------
-        // Negative weights of a column inside this unit's K range: counted by the producers while
-        // they decode (tail_neg, the slots past K, belongs to the split that holds the last k-tile),
-        // or read from the prefix counts that come with expanded weights.
-        const int* negc = s.negc[seq & 3];
-        const int tailc = (cur.t_end == p.ntiles) ? p.tail_neg : 0;
-        auto colcorr = [&](int col) -> int {
-            if (PRE) {
-                const int* np = p.negpre + cur.n0 + col;
-                return __ldg(np + (long long)cur.t_end * p.npad) - __ldg(np + (long long)cur.t_begin * p.npad);
-            }
-            return negc[col] - tailc;
-        };
-        auto part = [&](int i, int j, long long) -> int {
-            return s.accs[(i * TN + j) * WS_CONS + t] - ndrains * kMagicBits;
-        };
-        if (cur.tail_idx >= 0) {
-            // Tail split: every CTA of the tile leaves its partial sums (negative-weight correction
-            // included) in the workspace; the one that arrives last at the tile's counter adds them
-            // up -- in a fixed order, each thread its own 8 x TN outputs -- and applies the epilogue.
-            constexpr int SLOT = kTM * TN * WS_CONS;
-            int* base = p.partials + (long long)cur.tail_idx * p.tail_splits * SLOT;
-            int* mine = base + cur.sp * SLOT;
-#pragma unroll
-            for (int j = 0; j < TN; ++j) {
-                const int col = (TN == 8 && j >= 4) ? (BN / 2 + 4 * tn + j - 4) : (4 * tn + j);
-                const int corr = colcorr(col);
-#pragma unroll
-                for (int i = 0; i < kTM; ++i) __stcg(mine + (i * TN + j) * WS_CONS + t, part(i, j, 0) + corr);
-            }
-            __threadfence();
-            consumer_bar();
-            if (t == 0) {
-                int* cnt = p.counters + cur.tail_idx;
-                const int prev = atomicAdd(cnt, 1);
-                const int lastone = (prev == p.tail_splits - 1);
-                if (lastone) *cnt = 0;  // ready for the next launch
-                s.last_flag = lastone;
-            }
-            consumer_bar();
-            if (s.last_flag) {
-                __threadfence();
-                store_tile<TN, CONV>(
-                    p, cur.m0, cur.n0, tm, tn, BM, BN,
-                    [&](int i, int j, long long) -> int {
-                        int v = 0;
-                        for (int q = 0; q < p.tail_splits; ++q) v += __ldcg(base + q * SLOT + (i * TN + j) * WS_CONS + t);
-                        return v;
-                    },
-                    [&](int) -> int { return 0; });
-            }
-        } else if (p.splits == 1) {
-            store_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part, colcorr);
-        } else {
-            // split-K: add the partial sums into the zeroed output; the CTA that arrives last at
-            // this tile's counter reads the totals back and applies the epilogue in place.
-            reduce_tile<TN, CONV>(p, cur.m0, cur.n0, tm, tn, BM, BN, part, colcorr);
-            __threadfence();
-            consumer_bar();
-            if (t == 0) {
-                int* cnt = p.counters + cur.tile_id;
-                const int prev = atomicAdd(cnt, 1);
-                const int lastone = (prev == p.splits - 1);
-                if (lastone) *cnt = 0;  // ready for the next launch
-                s.last_flag = lastone;
-            }
-            consumer_bar();
-            if (s.last_flag) {
-                __threadfence();
-                const int* tot = static_cast<const int*>(p.out);
-                store_tile<TN, CONV>(
-                    p, cur.m0, cur.n0, tm, tn, BM, BN, [&](int, int, long long o) -> int { return __ldcg(tot + o); },
-                    [&](int) -> int { return 0; });
-            }
-        }
-        // All consumers have read this item's negative-weight counts before they are cleared for
-        // a later item (the producers are filling other sets meanwhile).
-        if (!PRE) {
-            consumer_bar();
-            for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
-        }
-    }
-    if (bad) g_ws_error = 1;
-}
-
-// Expands the packed weights of one launch into floats laid out as the k-tiles want them:
-// wd[t * bk + j][n] = +-2^-r, 0 for a zero weight and for every slot beyond K or N, and counts the
-// negative ones per (k-tile, column).  One thread per (column, k-tile), columns fastest.
-__global__ void __launch_bounds__(256) expand_weights_kernel(const GemmParams p, float* wd, int* negcnt)
-{
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long long)p.npad * p.ntiles) return;
-    const int t = int(idx / p.npad), n = int(idx - (long long)t * p.npad);
-    const uint32_t fmask = (1u << p.dec.fw) - 1u;
-    float* dst = wd + (long long)t * p.bk * p.npad + n;
-    int negs = 0;
-    for (int jw = 0; jw < p.kt_words; ++jw) {
-        const int word = t * p.kt_words + jw;
-        uint32_t w = 0;
-        const bool have = n < p.N && word < p.dec.row_len;
-        if (have) w = uint32_t(__ldg(p.packed + (long long)n * p.dec.row_len + word));
-        for (int i = 0; i < p.dec.num; ++i) {
-            const int k = word * p.dec.num + i;
-            int neg;
-            const float v = decode_f32(w & fmask, p.dec, have && k < p.K, neg);
-            w >>= p.dec.fw;
-            dst[(long long)(jw * p.dec.num + i) * p.npad] = v;
-            negs += neg;
-        }
-    }
-    negcnt[idx] = negs;
-}
-
-// Exclusive prefix sums of the per-tile counts along the k-tiles: row t of `negpre` becomes the
-// number of negative weights of the column in tiles 0 .. t-1, row ntiles the total.  A block
-// takes 32 columns; its 32 warps each sum one segment of the tiles, exchange the segment sums
-// through shared memory and then write the prefixes of their segment.
-__global__ void __launch_bounds__(1024) negative_prefix_kernel(const int* __restrict__ negcnt, int* __restrict__ negpre,
-                                                               int ntiles, int npad)
-{
-    __shared__ int seg[32][33];
-    const int lane = threadIdx.x, sg = threadIdx.y;
-    const int n = blockIdx.x * 32 + lane;
-    const bool live = n < npad;
-    const int per = (ntiles + 31) / 32;
-    const int t0 = min(ntiles, sg * per), t1 = min(ntiles, t0 + per);
-    int sum = 0;
-    if (live)
-        for (int t = t0; t < t1; ++t) sum += negcnt[(long long)t * npad + n];
-    seg[sg][lane] = sum;
-    __syncthreads();
-    int run = 0;
-    for (int q = 0; q < sg; ++q) run += seg[q][lane];
-    if (!live) return;
-    for (int t = t0; t < t1; ++t) {
-        negpre[(long long)t * npad + n] = run;
-        run += negcnt[(long long)t * npad + n];
-    }
-    if (sg == 31) negpre[(long long)ntiles * npad + n] = run;
-}
-
-// Chooses the k-tile: a multiple of num (whole packed words) and of the staging granularity
-// (row mode: UR whole rows; table mode: 4 columns), at most WS_BKT.
-template <int AM>
-bool ws_choose_tile(GemmParams& p)
-{
-    constexpr int KW = AM >= 1 ? AM : 1;
-    constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : (AM == AM_TABLE ? 4 : 1);
-    int best = 0;
-    for (int bk = WS_BKT; bk >= 2 && !best; --bk)
-        if (bk % p.dec.num == 0 && bk % GRAN == 0) best = bk;
-    if (!best) return false;
-    p.bk = best;
-    p.kt_words = best / p.dec.num;
-    p.rows_per_tile = best / KW;
-    p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
-    // Every slot from K to the end of the last tile decodes from a zero field, i.e. as -2^0.
-    p.tail_neg = p.ntiles * p.bk - p.K;
-    p.flush_tiles /= p.bk;  // the caller left the number of terms that cannot overflow
-    if (p.flush_tiles > 4096) p.flush_tiles = 4096;
-    return p.flush_tiles >= 1;
-}
-
-int num_sms()
-{
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    return sms;
-}
-
-// Sets the shared-memory attribute of one kernel instantiation once and checks that it can be used.
-template <int TN, int AM, bool PRE>
-int ws_kernel_ready()
-{
-    static int attr_state = 0;  // per instantiation: 0 unknown, 1 usable, -1 not usable
-    if (attr_state == 0) {
-        auto kern = ws_kernel<TN, AM, PRE>;
-        cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess ||
-            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(WsSmem<TN>))) !=
-                cudaSuccess) {
-            cudaGetLastError();
-            return DS_ERR_CUDA;
-        }
-        // The register hand-over in the kernel is sized for this launch allocation; with any
-        // other one the consumers could wait for registers for ever, so the kernel is not used.
-        attr_state = (fa.numRegs == WS_LAUNCH_REGS) ? 1 : -1;
-    }
-    return attr_state < 0 ? DS_ERR_UNSUPPORTED : DS_OK;
-}
-
-template <int TN, int AM>
-int ws_launch_cfg(GemmParams p, cudaStream_t st)
-{
-    using S = WsSmem<TN>;
-    if (!ws_choose_tile<AM>(p)) return DS_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(S);
-    if (int rc = ws_kernel_ready<TN, AM, false>()) return rc;
-    const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
-    if (gx * gy > 500000000LL) return DS_ERR_RANGE;
-    p.splits = 1;
-    p.tiles_per_split = p.ntiles;
-    p.tail_items = 0;
-    p.tail_splits = 1;
-    const long long tiles = gx * gy;
-    const int sms = num_sms();
-    constexpr long long SLOT_BYTES = (long long)kTM * TN * WS_CONS * 4;
-    // Expanded weights: when many row tiles would each decode the same packed words again, decode
-    // them once per launch into the front of the workspace (two small kernels ahead of this one).
-    p.npad = int(gy) * S::BN;
-    bool pre = false;
-    if (p.partials && gx >= 8) {
-        const long long wd_floats = (long long)p.ntiles * p.bk * p.npad;
-        const long long neg_ints = (long long)(p.ntiles + 1) * p.npad, cnt_ints = (long long)p.ntiles * p.npad;
-        const long long need = ((wd_floats + neg_ints + cnt_ints) * 4 + 255) / 256 * 256;
-        if (need <= p.partial_bytes && ws_kernel_ready<TN, AM, true>() == DS_OK) {
-            float* wd = reinterpret_cast<float*>(p.partials);
-            int* negpre = p.partials + wd_floats;
-            p.partials += need / 4;
-            p.partial_bytes -= need;
-            p.wd = wd;
-            p.negpre = negpre;
-            const long long threads = (long long)p.npad * p.ntiles;
-            int* negcnt = negpre + neg_ints;
-            expand_weights_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(p, wd, negcnt);
-            negative_prefix_kernel<<<(p.npad + 31) / 32, dim3(32, 32), 0, st>>>(negcnt, negpre, p.ntiles, p.npad);
-            if (cudaGetLastError() != cudaSuccess) return DS_ERR_CUDA;
-            pre = true;
-        }
-    }
-    if (p.counters && p.partials && p.ntiles >= 12 && tiles % sms != 0) {
-        // Tail split: the tiles beyond the last full wave are cut along K so that the CTAs which
-        // would idle during that wave share its work.  cost = length of the tail in tile times.
-        const long long full = tiles / sms * sms;
-        const int tail = int(tiles - full);
-        double best = 1.0;
-        for (int sp = 2; sp <= 4; ++sp) {
-            if (p.ntiles / sp < 4) break;
-            if ((long long)tail * sp * SLOT_BYTES > p.partial_bytes || tail > p.counter_slots) break;
-            const long long rounds = ((long long)tail * sp + sms - 1) / sms;
-            const double cost = double(rounds) / sp + 0.04;  // + writing and re-reading the partial sums
-            if (cost < best - 0.05) {
-                best = cost;
-                p.tail_splits = sp;
-            }
-        }
-        if (p.tail_splits > 1) {
-            p.tail_items = tail;
-            p.tail_first = int(full);
-            p.tail_tps = (p.ntiles + p.tail_splits - 1) / p.tail_splits;
-            p.tail_splits = (p.ntiles + p.tail_tps - 1) / p.tail_tps;
-        }
-    } else if (p.counters && !p.partials && tiles <= p.counter_slots && p.ntiles >= 16) {
-        // Split-K of every tile through integer atomics on the zeroed output, for callers whose
-        // workspace holds counters only: used when the tiles alone fill the SMs badly.
-        auto eff = [&](int sp) {
-            const long long ctas = tiles * sp, waves = (ctas + sms - 1) / sms;
-            return double(ctas) / double(waves * sms);
-        };
-        double best = eff(1);
-        for (int sp = 2; sp <= 4; ++sp) {
-            if (p.ntiles / sp < 8) break;
-            const double e = eff(sp) * 0.92;  // measured cost of zeroing, atomics and the second pass
-            if (e > best * 1.05) {
-                best = e;
-                p.splits = sp;
-            }
-        }
-        if (p.splits > 1) {
-            p.tiles_per_split = (p.ntiles + p.splits - 1) / p.splits;
-            p.splits = (p.ntiles + p.tiles_per_split - 1) / p.tiles_per_split;
-            if (cudaMemsetAsync(p.out, 0, size_t(p.M) * size_t(p.N) * 4, st) != cudaSuccess) return DS_ERR_CUDA;
-        }
-    }
-    p.grid_m = int(gx);
-    p.grid_n = int(gy);
-    p.full_units = p.tail_items ? p.tail_first : int(tiles * p.splits);
-    const long long items = (long long)p.full_units + (long long)p.tail_items * p.tail_splits;
-    const dim3 grid((unsigned)(items < sms ? items : sms));
-    if (pre) ws_kernel<TN, AM, true><<<grid, WS_NT, smem, st>>>(p);
-    else ws_kernel<TN, AM, false><<<grid, WS_NT, smem, st>>>(p);
-    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
-}
-
-template <int AM>
-int ws_launch_am(const GemmParams& p, cudaStream_t st)
-{
-    if (p.N > 64) return ws_launch_cfg<8, AM>(p, st);  // 256 x 128
-    return ws_launch_cfg<4, AM>(p, st);                // 256 x 64
-}
+constexpr int kMaxDevices = 64;
+int* g_ws_error_ptr[kMaxDevices];  // device address of the flag, looked up once per device
 
 }  // namespace
 
-int launch_ws(const GemmParams& p, int am, cudaStream_t st)
+int launch_ws(const GemmParams& p0, int am, cudaStream_t st)
 {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DS_ERR_CUDA;
+    if (!g_ws_error_ptr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_ws_error) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return DS_ERR_CUDA;
+        }
+        g_ws_error_ptr[dev] = static_cast<int*>(ptr);
+    }
+    GemmParams p = p0;
+    p.err_flag = g_ws_error_ptr[dev];
     switch (am) {
-        case AM_LINEAR: return ws_launch_am<AM_LINEAR>(p, st);
-        case AM_TABLE: return ws_launch_am<AM_TABLE>(p, st);
-        case 1: return ws_launch_am<1>(p, st);
-        case 3: return ws_launch_am<3>(p, st);
-        case 5: return ws_launch_am<5>(p, st);
-        case 7: return ws_launch_am<7>(p, st);
+        case AM_TABLE: return launch_ws_table(p, st);
+        case 1: return launch_ws_am1(p, st);
+        case 3: return launch_ws_am3(p, st);
+        case 5: return launch_ws_am5(p, st);
+        case 7: return launch_ws_am7(p, st);
         default: return DS_ERR_UNSUPPORTED;
     }
 }
