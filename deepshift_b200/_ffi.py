@@ -62,6 +62,8 @@ def lib():
         l.ds_strerror.argtypes = [ctypes.c_int]
         l.ds_strerror.restype = ctypes.c_char_p
         l.ds_version.restype = ctypes.c_int
+        l.ds_launch_count.argtypes = []
+        l.ds_launch_count.restype = ctypes.c_longlong
         _lib = l
     return _lib
 

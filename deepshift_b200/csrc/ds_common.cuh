@@ -7,6 +7,11 @@
 
 namespace ds {
 
+// Host-side count of the kernels this library has launched (ds_launch_count); every launch site
+// calls note_launch right after its <<<>>>.
+void note_launch(int n = 1);
+long long launch_count();
+
 // 1.5 * 2^23: a float in [2^23, 2^24) has ulp 1, so MAGIC + a (|a| < 2^22) keeps a as a
 // two's-complement integer in its low mantissa bits.
 constexpr float kMagic = 12582912.0f;

@@ -454,6 +454,7 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     const long long gx = ((long long)p.M + BM - 1) / BM, gy = (p.N + BN - 1) / BN;
     if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
     kern<<<dim3((unsigned)gx, (unsigned)gy), NT, smem, st>>>(p);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

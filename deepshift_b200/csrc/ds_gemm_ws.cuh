@@ -749,6 +749,7 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
             int* negcnt = negpre + neg_ints;
             expand_weights_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(p, wd, negcnt);
             negative_prefix_kernel<<<(p.npad + 31) / 32, dim3(32, 32), 0, st>>>(negcnt, negpre, p.ntiles, p.npad);
+            note_launch(2);
             if (cudaGetLastError() != cudaSuccess) return DS_ERR_CUDA;
             pre = true;
         }
@@ -804,6 +805,7 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     const dim3 grid((unsigned)(items < sms ? items : sms));
     if (pre) ws_kernel<TN, AM, true><<<grid, WS_NT, smem, st>>>(p);
     else ws_kernel<TN, AM, false><<<grid, WS_NT, smem, st>>>(p);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

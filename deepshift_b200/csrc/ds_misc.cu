@@ -3,6 +3,8 @@
 
 #include "ds_common.cuh"
 
+#include <atomic>
+
 namespace ds {
 namespace {
 
@@ -209,6 +211,12 @@ __global__ void __launch_bounds__(256) peak3_kernel(int iters, int seed, int* si
 
 }  // namespace
 
+static std::atomic<long long> g_launches{0};
+
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
 const char* status_string(int s)
 {
     switch (s) {
@@ -241,6 +249,7 @@ extern "C" int ds_compress(const int32_t* shiftp, const int32_t* sign, int32_t* 
     const int blocks = int(total / threads + 1 > 148 * 16 ? 148 * 16 : total / threads + 1);
     compress_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(shiftp, sign, packed, OC, K, bits,
                                                                              base, num, row_len);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
@@ -262,6 +271,7 @@ extern "C" int ds_quantize_f32(const float* x, int32_t* out, long long n, int ki
     const long long want = (n + threads - 1) / threads;
     const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
     quantize_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, n, kind, q);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
@@ -279,6 +289,7 @@ extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, in
     const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
     maxpool_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, total, H, W, OH, OW, k,
                                                                             stride, pad);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
@@ -293,6 +304,7 @@ extern "C" int ds_avgpool_fix_i32(const int32_t* x, int32_t* out, int B, int C, 
     const float scale = float(1ll << F);
     avgpool_fix_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, int(planes), H * W,
                                                                                 1.0f / scale, scale);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
@@ -318,6 +330,7 @@ extern "C" int ds_pipe_peak(int mode, int iters, double* ops_per_s, void* stream
         else if (mode == 4) peak2_kernel<4><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
         else if (mode == 5) peak3_kernel<5><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
         else peak3_kernel<6><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
+        note_launch();
     };
     run(iters / 8 + 1);  // warm-up
     cudaEventRecord(e0, st);
@@ -337,3 +350,6 @@ extern "C" int ds_pipe_peak(int mode, int iters, double* ops_per_s, void* stream
 
 extern "C" const char* ds_strerror(int status) { return status_string(status); }
 extern "C" int ds_version(void) { return 100; }
+
+// Kernels launched by this library in this process so far (host-side counter).
+extern "C" long long ds_launch_count(void) { return ds::launch_count(); }

@@ -127,6 +127,7 @@ int launch_small(const GemmParams& p, cudaStream_t st)
     splits = (nchunks + per - 1) / per;
     if (splits > 1 && cudaMemsetAsync(p.out, 0, size_t(p.M) * size_t(p.N) * 4, st) != cudaSuccess) return DS_ERR_CUDA;
     small_linear_kernel<MT, CPT><<<dim3(gx, gy, splits), SM_THREADS, 0, st>>>(p, per);
+    note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 

@@ -268,6 +268,7 @@ class IntPipeline:
             self.bias.append((w['bias'] * (2 ** self.F)).int().to(self.device).contiguous())
         self.x_in = torch.empty((batch,) + net.in_shape, dtype=torch.float32, device=self.device)
         self._plan()
+        self._n_launches = None
         self.graph = None
         if use_graph:
             self._capture()
@@ -370,14 +371,18 @@ class IntPipeline:
 
     @property
     def n_launches(self):
-        return len(self.calls)
+        """Kernels of this library in one pass, counted by the library itself while the pass was
+        recorded (a layer call can be several kernels: weight expansion, the convolution)."""
+        return len(self.calls) if self._n_launches is None else self._n_launches
 
     def _capture(self):
         with torch.cuda.device(self.device):
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
+                before = _ffi.lib().ds_launch_count()
                 self._launch_all()  # warm-up outside capture: sets kernel attributes
+                self._n_launches = int(_ffi.lib().ds_launch_count() - before)
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -393,5 +398,7 @@ class IntPipeline:
         if self.graph is not None:
             self.graph.replay()
         else:
+            before = _ffi.lib().ds_launch_count()
             self._launch_all()
+            self._n_launches = int(_ffi.lib().ds_launch_count() - before)
         return self.out

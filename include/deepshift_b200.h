@@ -202,6 +202,13 @@ int ds_pipe_peak(int mode, int iters, double *ops_per_s, void *stream);
  */
 int ds_last_kernel_error(int *flag);
 
+/*
+ * Number of kernels this library has launched in this process so far (a host-side counter;
+ * diagnostics, no counterpart in the reference).  The difference across one forward pass is the
+ * pass's kernel count, whatever path the launch heuristics took.
+ */
+long long ds_launch_count(void);
+
 const char *ds_strerror(int status);
 int ds_version(void);
 
