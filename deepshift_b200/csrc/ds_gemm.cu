@@ -458,6 +458,10 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
+// Few output channels and enough rows to fill the GPU with 512-row tiles: the 512 x 32 tile of
+// the block kernel beats the 256 x 64 tile of the warp-specialised one, half of which would be idle.
+inline bool narrow_tile(const GemmParams& p) { return p.N <= 32 && p.M >= 148 * 512; }
+
 // Tile shape by output width.  FP path: 256 rows x 128 or 64 columns, 512 threads.
 // Integer path: 128 x 128, 256 x 64 or 256 x 32, 256 threads.
 template <int AM>
@@ -467,6 +471,12 @@ int launch_am(const GemmParams& p, bool fp, cudaStream_t st)
         // Convolutions run on the warp-specialised kernel; the linear layer (x rows are
         // contiguous in k) stages faster with all 16 warps doing their share.
         if (AM != AM_LINEAR) {
+            // Few output channels: a 512 x 32 tile wastes no columns where the warp-specialised
+            // kernel would compute 64.
+            if (narrow_tile(p)) {
+                const int rc = launch_cfg<512, 64, 8, 4, 16, MODE_FP, AM>(p, st);
+                if (rc != DS_ERR_UNSUPPORTED) return rc;
+            }
             const int rc = launch_ws(p, AM, st);
             if (rc != DS_ERR_UNSUPPORTED) return rc;
         }
@@ -483,7 +493,15 @@ int launch_conv(const GemmParams& p, bool fp, cudaStream_t st)
     int rc = DS_ERR_UNSUPPORTED;
     switch (p.KW) {  // row mode where the window width has an instantiation and a k-tile exists
         case 1: rc = launch_am<1>(p, fp, st); break;
-        case 3: rc = launch_am<3>(p, fp, st); break;
+        case 3:
+            // stride 1 and padding 1 along W, rows of whole 16-byte groups: four pixels per load
+            if (fp && !narrow_tile(p) && p.sw == 1 && p.pw == 1 && p.W % 4 == 0 &&
+                (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0) {
+                rc = launch_ws(p, AM_QUAD3, st);
+                if (rc != DS_ERR_UNSUPPORTED) break;
+            }
+            rc = launch_am<3>(p, fp, st);
+            break;
         case 5: rc = launch_am<5>(p, fp, st); break;
         case 7: rc = launch_am<7>(p, fp, st); break;
         default: break;

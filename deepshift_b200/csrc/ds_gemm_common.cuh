@@ -11,6 +11,10 @@ constexpr int kTM = 8;  // rows of x per thread
 constexpr int kPadMarker = 0x7FC0DEAD;  // NaN pattern standing for "integer 0, do not quantise"
 constexpr int MODE_INT = 0, MODE_FP = 1;
 constexpr int AM_LINEAR = -1, AM_TABLE = 0;  // AM >= 1: row mode with KW = AM
+// Row mode for 3-wide windows with stride 1 and padding 1 along W, W a multiple of 4 and x 16-byte
+// aligned: a producer thread fetches four neighbouring pixels of a row with one 16-byte load plus
+// the two values beside them, and stores the three shifted copies as 16-byte vectors.
+constexpr int AM_QUAD3 = 13;
 
 struct GemmParams {
     const void* x;        // int32 or fp32
@@ -254,8 +258,8 @@ __device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
 // K with integer atomics when no epilogue is fused.
 int launch_small_linear(const GemmParams& p, cudaStream_t st);
 
-// Warp-specialised FP32-pipe convolution kernel (ds_gemm_ws.cuh).  am: AM_TABLE or the window
-// width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
+// Warp-specialised FP32-pipe convolution kernel (ds_gemm_ws.cuh).  am: AM_TABLE, AM_QUAD3 or the
+// window width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
 // then falls back to the table mode or the integer path.  The per-width entry points are what
 // launch_ws dispatches to; they expect GemmParams::err_flag to be set.
 int launch_ws(const GemmParams& p, int am, cudaStream_t st);
@@ -264,5 +268,6 @@ int launch_ws_am3(const GemmParams& p, cudaStream_t st);
 int launch_ws_am5(const GemmParams& p, cudaStream_t st);
 int launch_ws_am7(const GemmParams& p, cudaStream_t st);
 int launch_ws_table(const GemmParams& p, cudaStream_t st);
+int launch_ws_quad3(const GemmParams& p, cudaStream_t st);
 
 }  // namespace ds

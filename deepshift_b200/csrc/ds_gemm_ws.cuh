@@ -9,8 +9,8 @@
 //   * 8 producer warps (256 threads) gather x (implicit im2col, zero padding by predication,
 //     int32 -> x + 0.5 conversion or the fused fp32 quantiser), fetch the packed weight words
 //     and decode them through the lookup table, one k-tile ahead of the consumers.
-//   * The two groups meet only at mbarriers: full[s] (256 producer arrivals) and empty[s] (512
-//     consumer arrivals) for each of the two stages.  Global-load latency, the decode chains
+//   * The two groups meet only at mbarriers: full[s] (one arrival per producer warp) and empty[s]
+//     (one per consumer warp) for each of the two stages.  Global-load latency, the decode chains
 //     and the stores of a stage all overlap the FFMA stream of the previous stage, so the
 //     FMA pipe no longer idles while "everybody stages".
 //
@@ -66,6 +66,14 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count)
 __device__ __forceinline__ void mbar_arrive(unsigned long long* bar)
 {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One arrival for the whole warp: 32 arrivals on the same word would be served one after the
+// other.  __syncwarp orders every lane's shared-memory accesses before the elected lane's arrive.
+__device__ __forceinline__ void warp_arrive(unsigned long long* bar)
+{
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
 
 // Bounded wait for the phase with the given parity to complete.  Each try_wait lets the hardware
@@ -144,8 +152,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 {
     using S = WsSmem<TN>;
     constexpr bool CONV = AM != AM_LINEAR;
+    constexpr bool QUAD = AM == AM_QUAD3;
     constexpr bool ROW = AM >= 1;
-    constexpr int KW = ROW ? AM : 1;
+    constexpr int KW = QUAD ? 3 : (ROW ? AM : 1);
     constexpr int BM = WS_BM, BN = S::BN;
     constexpr int TMG = 32, TNG = 16;
     static_assert(offsetof(S, b) % 16 == 0 && offsetof(S, ktab) % 16 == 0 && offsetof(S, full) % 8 == 0, "alignment");
@@ -164,8 +173,8 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     for (int i = t; i < 4 * BN; i += WS_NT) (&s.negc[0][0])[i] = 0;
     if (t == 0) {
         for (int i = 0; i < WS_STAGES; ++i) {
-            mbar_init(&s.full[i], WS_PROD);
-            mbar_init(&s.empty[i], WS_CONS);
+            mbar_init(&s.full[i], WS_PROD / 32);   // one arrival per warp
+            mbar_init(&s.empty[i], WS_CONS / 32);
         }
         s.err = 0;
     }
@@ -198,7 +207,22 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // Per-item state of this thread: the x rows it gathers and the weight row it decodes.
         auto setup_item = [&](const WsItem& w) {
             wrow = (w.n0 + wn < p.N) ? p.packed + (long long)(w.n0 + wn) * p.dec.row_len : nullptr;
-            if (CONV) {
+            if (QUAD) {
+                // this thread's four pixels: same image, same output row, ow a multiple of 4
+                const int m = w.m0 + 4 * (pt & 63);
+                x_pix[0] = reinterpret_cast<const char*>(p.x);
+                rowmask[0] = colmask[0] = 0;
+                if (m < p.M) {
+                    const int b = m / p.P, pp = m - b * p.P;
+                    const int oh = pp / p.OW, ow = pp - oh * p.OW;
+                    const int ih0 = oh * p.sh - p.ph;
+                    for (int kh = 0; kh < p.KH; ++kh)
+                        if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[0] |= 1u << kh;
+                    colmask[0] = (ow > 0 ? 1u : 0u) | (ow + 4 < p.W ? 2u : 0u);  // value left / right of the four
+                    // address of (b, 0, ih0, ow): the centre tap of the first pixel
+                    x_pix[0] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + ow) * 4;
+                }
+            } else if (CONV) {
 #pragma unroll
                 for (int q = 0; q < PIX; ++q) {
                     const int m = w.m0 + pt + q * WS_PROD;
@@ -261,7 +285,27 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 }
             }
             const int tb = tile & 1;
-            if (ROW) {
+            if (QUAD) {
+                // thread = (four pixels, row group): rows rg, rg + 4 of the k-tile
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int2 e = *reinterpret_cast<const int2*>(&s.ktab[tb][(pt >> 6) + 4 * j]);
+                    const int* rowp = reinterpret_cast<const int*>(x_pix[0] + e.x);
+                    int4 c = make_int4(padv, padv, padv, padv);
+                    int l = padv, r = padv;
+                    if ((rowmask[0] >> e.y) & 1u) {  // rows past the tile: kh = 31
+                        c = __ldg(reinterpret_cast<const int4*>(rowp));
+                        if (colmask[0] & 1u) l = __ldg(rowp - 1);
+                        if (colmask[0] & 2u) r = __ldg(rowp + 4);
+                    }
+                    xr[6 * j + 0] = l;
+                    xr[6 * j + 1] = c.x;
+                    xr[6 * j + 2] = c.y;
+                    xr[6 * j + 3] = c.z;
+                    xr[6 * j + 4] = c.w;
+                    xr[6 * j + 5] = r;
+                }
+            } else if (ROW) {
 #pragma unroll
                 for (int u = 0; u < RMAX; ++u) {
                     const int2 e = *reinterpret_cast<const int2*>(&s.ktab[tb][u]);  // rows past the tile: kh = 31
@@ -310,7 +354,23 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         auto store_x = [&](auto ink_tag, auto last_tag, int st, int k0) {
             constexpr int INK = decltype(ink_tag)::value;
             constexpr bool LAST = decltype(last_tag)::value;
-            if (ROW) {
+            if (QUAD) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int u = (pt >> 6) + 4 * j;
+                    if (u < p.rows_per_tile) {
+                        float f[6];
+#pragma unroll
+                        for (int i = 0; i < 6; ++i) f[i] = operand_of<true, INK>(p, xr[6 * j + i]);
+#pragma unroll
+                        for (int kw = 0; kw < 3; ++kw) {
+                            float4 v = make_float4(f[kw], f[kw + 1], f[kw + 2], f[kw + 3]);
+                            if (LAST && k0 + u * 3 + kw >= p.K) v = make_float4(0.f, 0.f, 0.f, 0.f);
+                            *reinterpret_cast<float4*>(&s.a[st][u * 3 + kw][4 * (pt & 63)]) = v;
+                        }
+                    }
+                }
+            } else if (ROW) {
 #pragma unroll
                 for (int u = 0; u < RMAX; ++u) {
                     if (u < p.rows_per_tile) {
@@ -420,7 +480,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                         default: store_w(std::integral_constant<int, 16>(), st, negc); break;
                     }
                 }
-                mbar_arrive(&s.full[st]);
+                warp_arrive(&s.full[st]);
                 ++git;
                 // next (item, k-tile)
                 if (++tile >= cur.t_end) {
@@ -491,7 +551,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             if (p.bk == 24) k_loop(std::integral_constant<int, 24>());
             else if (p.bk == 28) k_loop(std::integral_constant<int, 28>());
             else k_loop(std::integral_constant<int, 0>());
-            mbar_arrive(&s.empty[st]);
+            warp_arrive(&s.empty[st]);
             if (++since == p.flush_tiles || it + 1 == my_tiles) {
                 // Move the float accumulators (raw bits, kMagicBits + A) into this thread's int32
                 // slots and restart them; the epilogue removes ndrains * kMagicBits.  The first
@@ -664,7 +724,7 @@ __global__ void __launch_bounds__(1024) negative_prefix_kernel(const int* __rest
 template <int AM>
 bool ws_choose_tile(GemmParams& p)
 {
-    constexpr int KW = AM >= 1 ? AM : 1;
+    constexpr int KW = AM == AM_QUAD3 ? 3 : (AM >= 1 ? AM : 1);
     constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : (AM == AM_TABLE ? 4 : 1);
     int best = 0;
     for (int bk = WS_BKT; bk >= 2 && !best; --bk)
