@@ -12,7 +12,9 @@ ours:       `value`  images/s with inputs resident in HBM (integer pipeline, CUD
             `e2e`    the same metric through the drop-in module API (LinearShift / Conv2dShift with
                      use_kernel=True) from pinned HOST input to HOST logits, copies inside the
                      timed region;
-            `roofline`, `cpu_baseline`, `clocks`, `gpu_launches` as described in DESIGN.md.
+            `roofline`  the 3x3 convolutions of one step, CUDA-event timed, against the live
+                     shift+add issue-rate probe; `cpu_baseline`, `clocks` (nvidia-smi samples during
+                     the timed region) and `gpu_launches` (counted by the library) beside it.
 reference:  the reference's own CPU kernels (oracle/_ref, else the C port of them) on the host
             cores, a bounded sample of the same workload per step.
 Prints exactly one JSON line on rank 0.

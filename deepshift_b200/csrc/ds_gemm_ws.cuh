@@ -550,6 +550,8 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             };
             if (p.bk == 24) k_loop(std::integral_constant<int, 24>());
             else if (p.bk == 28) k_loop(std::integral_constant<int, 28>());
+            else if (KW == 7 && p.bk == 21) k_loop(std::integral_constant<int, (KW == 7 ? 21 : 0)>());
+            else if (KW == 1 && p.bk == 16) k_loop(std::integral_constant<int, (KW == 1 ? 16 : 0)>());
             else k_loop(std::integral_constant<int, 0>());
             warp_arrive(&s.empty[st]);
             if (++since == p.flush_tiles || it + 1 == my_tiles) {
@@ -665,7 +667,8 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 
 // Expands the packed weights of one launch into floats laid out as the k-tiles want them:
 // wd[t * bk + j][n] = +-2^-r, 0 for a zero weight and for every slot beyond K or N, and counts the
-// negative ones per (k-tile, column).  One thread per (column, k-tile), columns fastest.
+// negative ones per (k-tile, column).  One thread per (column, k-tile), columns fastest.  bk need
+// not be a multiple of the weights per packed word.
 __global__ void __launch_bounds__(256) expand_weights_kernel(const GemmParams p, float* wd, int* negcnt)
 {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -673,20 +676,24 @@ __global__ void __launch_bounds__(256) expand_weights_kernel(const GemmParams p,
     const int t = int(idx / p.npad), n = int(idx - (long long)t * p.npad);
     const uint32_t fmask = (1u << p.dec.fw) - 1u;
     float* dst = wd + (long long)t * p.bk * p.npad + n;
-    int negs = 0;
-    for (int jw = 0; jw < p.kt_words; ++jw) {
-        const int word = t * p.kt_words + jw;
-        uint32_t w = 0;
-        const bool have = n < p.N && word < p.dec.row_len;
-        if (have) w = uint32_t(__ldg(p.packed + (long long)n * p.dec.row_len + word));
-        for (int i = 0; i < p.dec.num; ++i) {
-            const int k = word * p.dec.num + i;
+    const int32_t* row = p.packed + (long long)n * p.dec.row_len;
+    int negs = 0, have_word = -1;
+    uint32_t w = 0;
+    for (int j = 0; j < p.bk; ++j) {
+        const int k = t * p.bk + j;
+        const bool live = n < p.N && k < p.K;
+        float v = 0.0f;
+        if (live) {
+            const int word = k / p.dec.num, slot = k - word * p.dec.num;
+            if (word != have_word) {
+                w = uint32_t(__ldg(row + word));
+                have_word = word;
+            }
             int neg;
-            const float v = decode_f32(w & fmask, p.dec, have && k < p.K, neg);
-            w >>= p.dec.fw;
-            dst[(long long)(jw * p.dec.num + i) * p.npad] = v;
+            v = decode_f32((w >> (slot * p.dec.fw)) & fmask, p.dec, true, neg);
             negs += neg;
         }
+        dst[(long long)j * p.npad] = v;
     }
     negcnt[idx] = negs;
 }
@@ -719,23 +726,45 @@ __global__ void __launch_bounds__(1024) negative_prefix_kernel(const int* __rest
     if (sg == 31) negpre[(long long)ntiles * npad + n] = run;
 }
 
-// Chooses the k-tile: a multiple of num (whole packed words) and of the staging granularity
-// (row mode: UR whole rows; table mode: 4 columns), at most WS_BKT.
+// Chooses the k-tile, at most WS_BKT.  With packed weights decoded by the producers it is a
+// multiple of num (whole packed words) and of the staging granularity (row mode: UR whole rows;
+// table mode: 4 columns).  With expanded weights (`pre`) the row modes take any whole number of
+// rows: the one that pads K least (7x7 windows on 3 channels: 7 tiles of 21 instead of 6 of 28).
 template <int AM>
-bool ws_choose_tile(GemmParams& p)
+bool ws_choose_tile(GemmParams& p, bool pre)
 {
     constexpr int KW = AM == AM_QUAD3 ? 3 : (AM >= 1 ? AM : 1);
     constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : (AM == AM_TABLE ? 4 : 1);
+    constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows the producers have registers for
     int best = 0;
-    for (int bk = WS_BKT; bk >= 2 && !best; --bk)
-        if (bk % p.dec.num == 0 && bk % GRAN == 0) best = bk;
-    if (!best) return false;
-    p.bk = best;
-    p.kt_words = best / p.dec.num;
-    p.rows_per_tile = best / KW;
-    p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
-    // Every slot from K to the end of the last tile decodes from a zero field, i.e. as -2^0.
-    p.tail_neg = p.ntiles * p.bk - p.K;
+    if (pre && AM >= 1) {
+        long long best_padded = 0;
+        for (int rows = RMAX; rows >= 1; --rows) {
+            const int bk = rows * KW;
+            if (bk > WS_BKT || (bk < 12 && best)) continue;
+            const long long padded = ((long long)p.K + bk - 1) / bk * bk;
+            if (!best || padded < best_padded) {
+                best = bk;
+                best_padded = padded;
+            }
+        }
+        if (!best) return false;
+        p.bk = best;
+        p.kt_words = 0;  // not used: the producers copy expanded weights
+        p.rows_per_tile = best / KW;
+        p.ntiles = (p.K + best - 1) / best;
+        p.tail_neg = 0;  // expanded weights are 0 beyond K
+    } else {
+        for (int bk = WS_BKT; bk >= 2 && !best; --bk)
+            if (bk % p.dec.num == 0 && bk % GRAN == 0) best = bk;
+        if (!best) return false;
+        p.bk = best;
+        p.kt_words = best / p.dec.num;
+        p.rows_per_tile = best / KW;
+        p.ntiles = (p.dec.row_len + p.kt_words - 1) / p.kt_words;
+        // Every slot from K to the end of the last tile decodes from a zero field, i.e. as -2^0.
+        p.tail_neg = p.ntiles * p.bk - p.K;
+    }
     p.flush_tiles /= p.bk;  // the caller left the number of terms that cannot overflow
     if (p.flush_tiles > 4096) p.flush_tiles = 4096;
     return p.flush_tiles >= 1;
@@ -778,27 +807,22 @@ template <int TN, int AM>
 int ws_launch_cfg(GemmParams p, cudaStream_t st)
 {
     using S = WsSmem<TN>;
-    if (!ws_choose_tile<AM>(p)) return DS_ERR_UNSUPPORTED;
     const size_t smem = sizeof(S);
-    if (int rc = ws_kernel_ready<TN, AM, false>()) return rc;
     const long long gx = ((long long)p.M + WS_BM - 1) / WS_BM, gy = (p.N + S::BN - 1) / S::BN;
     if (gx * gy > 500000000LL) return DS_ERR_RANGE;
-    p.splits = 1;
-    p.tiles_per_split = p.ntiles;
-    p.tail_items = 0;
-    p.tail_splits = 1;
     const long long tiles = gx * gy;
     const int sms = num_sms();
     constexpr long long SLOT_BYTES = (long long)kTM * TN * WS_CONS * 4;
     // Expanded weights: when many row tiles would each decode the same packed words again, decode
     // them once per launch into the front of the workspace (two small kernels ahead of this one).
-    p.npad = int(gy) * S::BN;
+    const GemmParams p_in = p;
     bool pre = false;
-    if (p.partials && gx >= 8) {
+    if (p.partials && gx >= 8 && ws_kernel_ready<TN, AM, true>() == DS_OK && ws_choose_tile<AM>(p, true)) {
+        p.npad = int(gy) * S::BN;
         const long long wd_floats = (long long)p.ntiles * p.bk * p.npad;
         const long long neg_ints = (long long)(p.ntiles + 1) * p.npad, cnt_ints = (long long)p.ntiles * p.npad;
         const long long need = ((wd_floats + neg_ints + cnt_ints) * 4 + 255) / 256 * 256;
-        if (need <= p.partial_bytes && ws_kernel_ready<TN, AM, true>() == DS_OK) {
+        if (need <= p.partial_bytes) {
             float* wd = reinterpret_cast<float*>(p.partials);
             int* negpre = p.partials + wd_floats;
             p.partials += need / 4;
@@ -814,6 +838,16 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
             pre = true;
         }
     }
+    if (!pre) {
+        p = p_in;
+        if (!ws_choose_tile<AM>(p, false)) return DS_ERR_UNSUPPORTED;
+        if (int rc = ws_kernel_ready<TN, AM, false>()) return rc;
+        p.npad = int(gy) * S::BN;
+    }
+    p.splits = 1;
+    p.tiles_per_split = p.ntiles;
+    p.tail_items = 0;
+    p.tail_splits = 1;
     if (p.counters && p.partials && p.ntiles >= 12 && tiles % sms != 0) {
         // Tail split: the tiles beyond the last full wave are cut along K so that the CTAs which
         // would idle during that wave share its work.  cost = length of the tail in tile times.

@@ -251,6 +251,11 @@ def test_pooling_on_codes(cuda_device):
     for k, s, p in [(2, 2, 0), (3, 2, 1)]:
         ref = torch.nn.functional.max_pool2d(xt.double(), k, s, p).to(torch.int32)
         assert torch.equal(kernels.maxpool2d_i32(xt, k, s, p), ref)
+    # widths that are a multiple of 8 take the four-outputs-per-thread kernel of the 3x3/2/1 pool
+    for shape in [(2, 3, 16, 16), (1, 2, 9, 24), (2, 1, 112, 112)]:
+        y = _t(rng.integers(-40000, 40000, shape).astype(np.int32), cuda_device)
+        ref = torch.nn.functional.max_pool2d(y.double(), 3, 2, 1).to(torch.int32)
+        assert torch.equal(kernels.maxpool2d_i32(y, 3, 2, 1), ref)
     F = 12
     got = kernels.avgpool_fix_i32(xt, F).cpu().numpy()
     mean = (x.astype(np.int64).sum(axis=(2, 3)).astype(np.float32) / np.float32(1 << F)) / np.float32(169)
