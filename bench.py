@@ -313,11 +313,11 @@ def run_ours(args, rank, world, local):
                     "frac": dom_bytes / (dom_ms * 1e-3) / 1e9 / hbm_peak, "peak_source": hbm_src,
                     "algorithmic_bytes_per_step": dom_bytes},
             # ncu dram__bytes_read+write of two full-size launches of this kernel (profiles/
-            # ws_kernel_dram_traffic_full_size.md): 161.3 MB vs 205.7 MB algorithmic (128ch 28x28) and
-            # 367.9 MB vs 411.2 MB (64ch 56x56) -> 0.858 of the algorithmic bytes; x is read exactly
+            # ws_kernel_dram_traffic_full_size.md): 172.6 MB vs 205.7 MB algorithmic (128ch 28x28) and
+            # 373.5 MB vs 411.2 MB (64ch 56x56) -> 0.885 of the algorithmic bytes; x is read exactly
             # once, part of the output is still in L2 when the kernel ends.
-            "traffic": 0.858 * dom_bytes / dom_n,
-            "traffic_note": "bytes per launch = 0.858 x algorithmic bytes per launch (ncu, full-size layers)",
+            "traffic": 0.885 * dom_bytes / dom_n,
+            "traffic_note": "bytes per launch = 0.885 x algorithmic bytes per launch (ncu, full-size layers)",
         }
 
     if rank != 0:
