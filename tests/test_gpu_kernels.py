@@ -354,6 +354,38 @@ def test_conv_tail_wave_is_split(oracle, cuda_device, B):
     assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("shape", [(12, 16, 28, 28, 40, 3, 1, 1),    # four-pixel staging, 37 row tiles
+                                   (9, 3, 60, 60, 24, 7, 2, 3),      # 7-wide rows: k-tiles of 21 with a workspace
+                                   (11, 40, 30, 30, 96, 1, 2, 0),    # 1x1, stride 2
+                                   (10, 12, 26, 30, 70, 3, 1, 1)])   # 3x3 on a width that is no multiple of 4
+def test_conv_with_and_without_workspace_agree(oracle, cuda_device, shape):
+    """The same convolution through ds_conv2d_ex with the Python layer's workspace (weights
+    expanded once per launch, k-tile free of the packed-word size, tail tiles shared) and
+    through ds_conv2d_i32 without any (the producers decode the packed words): same bits, and
+    the library counts three kernels for the first and one for the second."""
+    from deepshift_b200 import _ffi, kernels
+    B, C, H, W, OC, k, s, p = shape
+    rng = np.random.default_rng(sum(shape))
+    x = acts_q16(rng, (B, C, H, W))
+    shift, sign = weights(rng, (OC, C, k, k))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    xt, bt = _t(x, cuda_device), _t(bias, cuda_device)
+    lib = _ffi.lib()
+    n0 = lib.ds_launch_count()
+    with_ws = kernels.conv2d(xt, _t(shift, cuda_device), None, bt, cw, s, p, act_bits=16)
+    n1 = lib.ds_launch_count()
+    OH, OW = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+    plain = torch.empty((B, OC, OH, OW), dtype=torch.int32, device=cuda_device)
+    rc = lib.ds_conv2d_i32(xt.data_ptr(), cw.data.data_ptr(), bt.data_ptr(), plain.data_ptr(), B, C, H, W, OC,
+                           k, k, s, s, p, p, cw.bits, cw.base, 16, torch.cuda.current_stream().cuda_stream)
+    n2 = lib.ds_launch_count()
+    assert rc == 0
+    assert torch.equal(with_ws, plain)
+    assert np.array_equal(plain.cpu().numpy(), oracle.conv2d(x, shift, sign, bias, (s, s), (p, p)))
+    assert (n1 - n0, n2 - n1) == (3, 1)
+
+
 def test_plain_c_abi_entry_points(oracle, cuda_device):
     """ds_linear_i32 / ds_conv2d_i32 called directly with raw pointers, as a foreign-language
     binding would (no fused options, no workspace)."""
