@@ -29,10 +29,18 @@ constexpr int WS_BM = 256;     // rows of x per CTA
 constexpr int WS_BKT = 28;     // largest k-tile
 constexpr int WS_STAGES = 2;
 // Register split after the roles part.  The CTA starts with 768 * 80 registers; what the
-// producers give back (256 * (80 - 56) = 6144) is all the consumers can take (512 * (88 - 80) =
-// 4096): a larger request would wait for registers that never come.
-constexpr int WS_LAUNCH_REGS = 80, WS_PROD_REGS = 56, WS_CONS_REGS = 88;
-static_assert(WS_CONS * (WS_CONS_REGS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - WS_PROD_REGS), "register pool");
+// producers give back is all the consumers can take: a larger request would wait for registers
+// that never come.  Usual split 56 / 88 (256 * 24 >= 512 * 8).  The four-pixel staging mode needs
+// fewer producer registers, so its split is 48 / 96 (256 * 32 = 512 * 16): with 96 registers the
+// compiler has room to fetch the next fragments early, and a consumer warp running without its
+// neighbours (which wait at the hand-shake) keeps the FMA pipe busier.
+constexpr int WS_LAUNCH_REGS = 80;
+template <int AM>
+struct WsRegs {
+    static constexpr int PROD = (AM == AM_QUAD3) ? 48 : 56;
+    static constexpr int CONS = (AM == AM_QUAD3) ? 96 : 88;
+    static_assert(WS_CONS * (CONS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - PROD), "register pool");
+};
 constexpr int WS_WAIT_LIMIT = 1 << 12;  // rounds of one mbarrier wait before giving up
 constexpr unsigned WS_WAIT_NS = 1000000;  // suspend-time hint of one round, nanoseconds
 
@@ -182,7 +190,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 
     if (t >= WS_CONS) {
         // =========================== producers ==================================================
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WS_PROD_REGS));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WsRegs<AM>::PROD));
         const int pt = t - WS_CONS;
         constexpr int PIX = BM / WS_PROD;  // rows of the x tile per producer thread (conv)
         const char* x_pix[PIX];
@@ -501,7 +509,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     }
 
     // =============================== consumers ====================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WS_CONS_REGS));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WsRegs<AM>::CONS));
     // A warp covers 8 x 4 thread tiles, 8 along the direction in which the output is contiguous.
     const int lane = t & 31, warp = t >> 5;
     int tm, tn;
