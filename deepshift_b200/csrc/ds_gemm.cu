@@ -500,6 +500,11 @@ int launch_conv(const GemmParams& p, bool fp, cudaStream_t st)
                 rc = launch_ws(p, AM_QUAD3, st);
                 if (rc != DS_ERR_UNSUPPORTED) break;
             }
+            if (fp && !narrow_tile(p) && p.sw == 1 && p.pw == 1 && p.W % 2 == 0 &&
+                (reinterpret_cast<uintptr_t>(p.x) & 7u) == 0) {  // two pixels per 8-byte load
+                rc = launch_ws(p, AM_PAIR3, st);
+                if (rc != DS_ERR_UNSUPPORTED) break;
+            }
             rc = launch_am<3>(p, fp, st);
             break;
         case 5: rc = launch_am<5>(p, fp, st); break;

@@ -15,6 +15,8 @@ constexpr int AM_LINEAR = -1, AM_TABLE = 0;  // AM >= 1: row mode with KW = AM
 // aligned: a producer thread fetches four neighbouring pixels of a row with one 16-byte load plus
 // the two values beside them, and stores the three shifted copies as 16-byte vectors.
 constexpr int AM_QUAD3 = 13;
+// The same for W a multiple of 2 only and x 8-byte aligned: two pixels per 8-byte load.
+constexpr int AM_PAIR3 = 23;
 
 struct GemmParams {
     const void* x;        // int32 or fp32
@@ -269,5 +271,6 @@ int launch_ws_am5(const GemmParams& p, cudaStream_t st);
 int launch_ws_am7(const GemmParams& p, cudaStream_t st);
 int launch_ws_table(const GemmParams& p, cudaStream_t st);
 int launch_ws_quad3(const GemmParams& p, cudaStream_t st);
+int launch_ws_pair3(const GemmParams& p, cudaStream_t st);
 
 }  // namespace ds

@@ -161,8 +161,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     using S = WsSmem<TN>;
     constexpr bool CONV = AM != AM_LINEAR;
     constexpr bool QUAD = AM == AM_QUAD3;
+    constexpr bool PAIR = AM == AM_PAIR3;
     constexpr bool ROW = AM >= 1;
-    constexpr int KW = QUAD ? 3 : (ROW ? AM : 1);
+    constexpr int KW = (QUAD || PAIR) ? 3 : (ROW ? AM : 1);
     constexpr int BM = WS_BM, BN = S::BN;
     constexpr int TMG = 32, TNG = 16;
     static_assert(offsetof(S, b) % 16 == 0 && offsetof(S, ktab) % 16 == 0 && offsetof(S, full) % 8 == 0, "alignment");
@@ -228,6 +229,20 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                         if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[0] |= 1u << kh;
                     colmask[0] = (ow > 0 ? 1u : 0u) | (ow + 4 < p.W ? 2u : 0u);  // value left / right of the four
                     // address of (b, 0, ih0, ow): the centre tap of the first pixel
+                    x_pix[0] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + ow) * 4;
+                }
+            } else if (PAIR) {
+                // this thread's two pixels: same image, same output row, ow even
+                const int m = w.m0 + 2 * (pt & 127);
+                x_pix[0] = reinterpret_cast<const char*>(p.x);
+                rowmask[0] = colmask[0] = 0;
+                if (m < p.M) {
+                    const int b = m / p.P, pp = m - b * p.P;
+                    const int oh = pp / p.OW, ow = pp - oh * p.OW;
+                    const int ih0 = oh * p.sh - p.ph;
+                    for (int kh = 0; kh < p.KH; ++kh)
+                        if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[0] |= 1u << kh;
+                    colmask[0] = (ow > 0 ? 1u : 0u) | (ow + 2 < p.W ? 2u : 0u);  // value left / right of the two
                     x_pix[0] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + ow) * 4;
                 }
             } else if (CONV) {
@@ -313,6 +328,24 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     xr[6 * j + 4] = c.w;
                     xr[6 * j + 5] = r;
                 }
+            } else if (PAIR) {
+                // thread = (two pixels, row group): rows rg, rg + 2, rg + 4, rg + 6 of the k-tile
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int2 e = *reinterpret_cast<const int2*>(&s.ktab[tb][(pt >> 7) + 2 * j]);
+                    const int* rowp = reinterpret_cast<const int*>(x_pix[0] + e.x);
+                    int2 c = make_int2(padv, padv);
+                    int l = padv, r = padv;
+                    if ((rowmask[0] >> e.y) & 1u) {  // rows past the tile: kh = 31
+                        c = __ldg(reinterpret_cast<const int2*>(rowp));
+                        if (colmask[0] & 1u) l = __ldg(rowp - 1);
+                        if (colmask[0] & 2u) r = __ldg(rowp + 2);
+                    }
+                    xr[4 * j + 0] = l;
+                    xr[4 * j + 1] = c.x;
+                    xr[4 * j + 2] = c.y;
+                    xr[4 * j + 3] = r;
+                }
             } else if (ROW) {
 #pragma unroll
                 for (int u = 0; u < RMAX; ++u) {
@@ -375,6 +408,22 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                             float4 v = make_float4(f[kw], f[kw + 1], f[kw + 2], f[kw + 3]);
                             if (LAST && k0 + u * 3 + kw >= p.K) v = make_float4(0.f, 0.f, 0.f, 0.f);
                             *reinterpret_cast<float4*>(&s.a[st][u * 3 + kw][4 * (pt & 63)]) = v;
+                        }
+                    }
+                }
+            } else if (PAIR) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int u = (pt >> 7) + 2 * j;
+                    if (u < p.rows_per_tile) {
+                        float f[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) f[i] = operand_of<true, INK>(p, xr[4 * j + i]);
+#pragma unroll
+                        for (int kw = 0; kw < 3; ++kw) {
+                            float2 v = make_float2(f[kw], f[kw + 1]);
+                            if (LAST && k0 + u * 3 + kw >= p.K) v = make_float2(0.f, 0.f);
+                            *reinterpret_cast<float2*>(&s.a[st][u * 3 + kw][2 * (pt & 127)]) = v;
                         }
                     }
                 }
@@ -741,7 +790,7 @@ __global__ void __launch_bounds__(1024) negative_prefix_kernel(const int* __rest
 template <int AM>
 bool ws_choose_tile(GemmParams& p, bool pre)
 {
-    constexpr int KW = AM == AM_QUAD3 ? 3 : (AM >= 1 ? AM : 1);
+    constexpr int KW = (AM == AM_QUAD3 || AM == AM_PAIR3) ? 3 : (AM >= 1 ? AM : 1);
     constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : (AM == AM_TABLE ? 4 : 1);
     constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows the producers have registers for
     int best = 0;
