@@ -22,6 +22,7 @@ class Fuse(ctypes.Structure):
         ("residual", ctypes.c_void_p), ("act_bits", ctypes.c_int),
         ("round_f32", ctypes.c_int), ("reserved", ctypes.c_int * 3),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_longlong),
+        ("prepared", ctypes.c_void_p), ("prepared_bytes", ctypes.c_longlong),
     ]
 
 
@@ -35,6 +36,7 @@ _SIGNATURES = {
     "ds_linear_ex": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, ctypes.POINTER(Fuse), _VP],
     "ds_conv2d_ex": [_VP, _VP, _VP, _VP] + [_I] * 13 + [ctypes.POINTER(Fuse), _VP],
     "ds_conv2d_noalloc": [_VP, _VP, _VP, _VP] + [_I] * 13 + [ctypes.POINTER(Fuse), _VP],
+    "ds_conv2d_prepare": [_VP] + [_I] * 13 + [ctypes.POINTER(Fuse), ctypes.POINTER(ctypes.c_longlong), _VP],
     "ds_compress": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "ds_quantize_f32": [_VP, _VP, _LL, _I, _I, _I, _VP],
     "ds_maxpool2d_i32": [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],

@@ -441,6 +441,7 @@ int launch_cfg(GemmParams p, cudaStream_t st)
         if (p.flush_tiles < 1) return DS_ERR_UNSUPPORTED;
         if (p.flush_tiles > 4096) p.flush_tiles = 4096;
     }
+    if (p.prepare_only) return DS_OK;  // this kernel decodes the packed words itself
     auto kern = gemm_kernel<NT, TMG, TNG, TN, BKT, MODE, AM>;
     const size_t smem = sizeof(S);
     static bool attr_done = false;  // per instantiation
@@ -551,6 +552,9 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.wd = nullptr;
     p.negpre = nullptr;
     p.npad = 0;
+    p.prepared = f.prepared;
+    p.prepared_bytes = f.prepared ? f.prepared_bytes : 0;
+    if (f.prepared && ((reinterpret_cast<uintptr_t>(f.prepared) & 15u) || f.prepared_bytes < 0)) return DS_ERR_BAD_ARG;
     p.full_units = p.tail_first = p.tail_items = 0;
     p.tail_splits = 1;
     p.tail_tps = 0;
@@ -617,18 +621,27 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     return launch_am<AM_LINEAR>(p, fp, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t* bias, void* out, int B,
-                            int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
-                            int bits, int base, const ds_fuse_t* fuse, void* stream)
+namespace ds {
+namespace {
+
+// Shared body of ds_conv2d_ex and ds_conv2d_prepare.
+int conv2d_run(const void* x, const int32_t* packed, const int32_t* bias, void* out, int B, int C, int H, int W,
+               int OC, int KH, int KW, int sh, int sw, int ph, int pw, int bits, int base, const ds_fuse_t* fuse,
+               void* stream, long long* needed_out)
 {
+    const bool prepare = needed_out != nullptr;
     if (B < 0 || C <= 0 || H <= 0 || W <= 0 || OC <= 0 || KH <= 0 || KW <= 0 || sh <= 0 || sw <= 0 ||
         ph < 0 || pw < 0)
         return DS_ERR_BAD_ARG;
     if (KH > 31 || KW > 31) return DS_ERR_UNSUPPORTED;
     if (H + 2 * ph < KH || W + 2 * pw < KW) return DS_ERR_BAD_ARG;
     if (B == 0) return DS_OK;
-    int rc = check_ptrs(x, packed, out);
-    if (rc) return rc;
+    if (prepare) {
+        if (!packed || (reinterpret_cast<uintptr_t>(packed) & 3u)) return DS_ERR_BAD_ARG;
+    } else {
+        const int rc = check_ptrs(x, packed, out);
+        if (rc) return rc;
+    }
     const int OH = (H + 2 * ph - KH) / sh + 1, OW = (W + 2 * pw - KW) / sw + 1;
     const long long M = (long long)B * OH * OW, Kll = (long long)C * KH * KW;
     if (M > 2147483647LL || Kll > 2147483647LL || (long long)C * H * W > 2147483647LL) return DS_ERR_RANGE;
@@ -643,9 +656,32 @@ extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t*
     p.magic_kw = magic_of(KW);
     p.magic_kh = magic_of(KH);
     bool fp = false;
-    rc = setup_common(p, bits, base, fuse, fp);
+    const int rc = setup_common(p, bits, base, fuse, fp);
     if (rc) return rc;
+    p.prepare_only = prepare ? 1 : 0;
+    p.needed_out = needed_out;
     return launch_conv(p, fp, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace ds
+
+extern "C" int ds_conv2d_ex(const void* x, const int32_t* packed, const int32_t* bias, void* out, int B,
+                            int C, int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
+                            int bits, int base, const ds_fuse_t* fuse, void* stream)
+{
+    return ds::conv2d_run(x, packed, bias, out, B, C, H, W, OC, KH, KW, sh, sw, ph, pw, bits, base, fuse, stream,
+                          nullptr);
+}
+
+extern "C" int ds_conv2d_prepare(const int32_t* packed, int B, int C, int H, int W, int OC, int KH, int KW,
+                                 int sh, int sw, int ph, int pw, int bits, int base, const ds_fuse_t* fuse,
+                                 long long* bytes_needed, void* stream)
+{
+    if (!bytes_needed) return DS_ERR_BAD_ARG;
+    *bytes_needed = 0;
+    return ds::conv2d_run(nullptr, packed, nullptr, nullptr, B, C, H, W, OC, KH, KW, sh, sw, ph, pw, bits, base,
+                          fuse, stream, bytes_needed);
 }
 
 extern "C" int ds_linear_i32(const int32_t* x, const int32_t* packed, const int32_t* bias, int32_t* out,

@@ -57,6 +57,11 @@ struct GemmParams {
     const int* negpre;   // [ntiles + 1][npad]: negative weights of a column in the k-tiles before t
     int npad;            // grid_n * BN
     int* err_flag;       // set to 1 by a kernel whose bounded wait ran out
+    // weights expanded ahead of time by the caller (ds_conv2d_prepare)
+    const void* prepared;
+    long long prepared_bytes;
+    int prepare_only;        // this call only fills `prepared` (or reports its size), no convolution
+    long long* needed_out;   // host: receives the bytes `prepared` needs for this geometry
     Quant q;
     int rq_lo, rq_hi;
     float inv_scale;  // 2^-F

@@ -874,27 +874,45 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
     // them once per launch into the front of the workspace (two small kernels ahead of this one).
     const GemmParams p_in = p;
     bool pre = false;
-    if (p.partials && gx >= 8 && ws_kernel_ready<TN, AM, true>() == DS_OK && ws_choose_tile<AM>(p, true)) {
+    if ((p.partials || p.prepared || p.prepare_only) && gx >= 8 && ws_kernel_ready<TN, AM, true>() == DS_OK &&
+        ws_choose_tile<AM>(p, true)) {
         p.npad = int(gy) * S::BN;
         const long long wd_floats = (long long)p.ntiles * p.bk * p.npad;
         const long long neg_ints = (long long)(p.ntiles + 1) * p.npad, cnt_ints = (long long)p.ntiles * p.npad;
         const long long need = ((wd_floats + neg_ints + cnt_ints) * 4 + 255) / 256 * 256;
-        if (need <= p.partial_bytes) {
-            float* wd = reinterpret_cast<float*>(p.partials);
-            int* negpre = p.partials + wd_floats;
-            p.partials += need / 4;
-            p.partial_bytes -= need;
+        auto expand_into = [&](int* base) {
+            float* wd = reinterpret_cast<float*>(base);
+            int* negpre = base + wd_floats;
+            int* negcnt = negpre + neg_ints;
             p.wd = wd;
             p.negpre = negpre;
             const long long threads = (long long)p.npad * p.ntiles;
-            int* negcnt = negpre + neg_ints;
             expand_weights_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(p, wd, negcnt);
             negative_prefix_kernel<<<(p.npad + 31) / 32, dim3(32, 32), 0, st>>>(negcnt, negpre, p.ntiles, p.npad);
             note_launch(2);
-            if (cudaGetLastError() != cudaSuccess) return DS_ERR_CUDA;
+            return cudaGetLastError() == cudaSuccess;
+        };
+        if (p.prepare_only) {
+            // ds_conv2d_prepare: report the size; fill the caller's buffer if there is one
+            *p.needed_out = need;
+            if (!p.prepared) return DS_OK;
+            if (need > p.prepared_bytes) return DS_ERR_SCRATCH;
+            return expand_into(static_cast<int*>(const_cast<void*>(p.prepared))) ? DS_OK : DS_ERR_CUDA;
+        }
+        if (p.prepared && need <= p.prepared_bytes) {
+            // expanded ahead of time for this geometry: same layout as expand_into writes
+            p.wd = static_cast<const float*>(p.prepared);
+            p.negpre = static_cast<const int*>(p.prepared) + wd_floats;
+            pre = true;
+        } else if (p.partials && need <= p.partial_bytes) {
+            int* base = p.partials;
+            p.partials += need / 4;
+            p.partial_bytes -= need;
+            if (!expand_into(base)) return DS_ERR_CUDA;
             pre = true;
         }
     }
+    if (p.prepare_only) return DS_OK;  // this geometry does not use expanded weights
     if (!pre) {
         p = p_in;
         if (!ws_choose_tile<AM>(p, false)) return DS_ERR_UNSUPPORTED;

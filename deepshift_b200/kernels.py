@@ -15,6 +15,8 @@ Differences from the reference, all deliberate:
     encoding of utils.py:67-70; the reference CUDA kernel yields -1 for negative inputs);
   * ``dilation != 1`` or ``groups != 1`` raises instead of being ignored (kernels.py:28).
 """
+import ctypes
+
 import torch
 
 from . import _ffi
@@ -174,6 +176,30 @@ def linear_fused(input, out_features, bias_i32, conc_weight, *, in_kind=_ffi.IN_
     return out
 
 
+def _prepared_weights(conc_weight, geometry, fuse, device):
+    """The layer's weights expanded once for this geometry and arithmetic path (ds_conv2d_prepare),
+    kept on the ``ConcWeight`` they were made from: a new ``ConcWeight`` (re-packed weights) starts
+    with an empty cache; packed data changed in place would not be noticed.  None when launches of
+    this geometry do not use expanded weights."""
+    cache = conc_weight.__dict__.setdefault("_prepared", {})
+    key = geometry + (fuse.in_kind, fuse.act_bits, fuse.act_integer_bits, fuse.act_fraction_bits,
+                      conc_weight.data.data_ptr(), str(device))
+    if key not in cache:
+        lib, need = _ffi.lib(), ctypes.c_longlong(0)
+        args = (conc_weight.data.data_ptr(),) + geometry + (conc_weight.bits, conc_weight.base)
+        fuse.prepared, fuse.prepared_bytes = None, 0
+        _ffi.check(lib.ds_conv2d_prepare(*args, fuse, ctypes.byref(need), _stream_ptr(device)), "conv2d_prepare")
+        buf = None
+        if need.value > 0:
+            buf = torch.empty(need.value // 4, dtype=torch.int32, device=device)
+            fuse.prepared, fuse.prepared_bytes = buf.data_ptr(), need.value
+            _ffi.check(lib.ds_conv2d_prepare(*args, fuse, ctypes.byref(need), _stream_ptr(device)),
+                       "conv2d_prepare")
+            fuse.prepared, fuse.prepared_bytes = None, 0
+        cache[key] = buf
+    return cache[key]
+
+
 def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0, *, in_kind=_ffi.IN_I32,
                  out_kind=_ffi.OUT_I32, act_integer_bits=16, act_fraction_bits=16, relu=False, requant=False,
                  residual=None, act_bits=0, round_f32=False, out=None):
@@ -194,7 +220,12 @@ def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0
             raise RuntimeError("residual shape %s != output shape %s" % (tuple(residual.shape), tuple(out.shape)))
     f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32,
               workspace(input.device))
+    geometry = (B, C, H, W, OC, KH, KW, sh, sw, ph, pw)
     with torch.cuda.device(input.device):
+        prepared = _prepared_weights(conc_weight, geometry, f, input.device)
+        if prepared is not None:
+            f.prepared = prepared.data_ptr()
+            f.prepared_bytes = prepared.numel() * 4
         rc = _ffi.lib().ds_conv2d_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),
                                      B, C, H, W, OC, KH, KW, sh, sw, ph, pw, conc_weight.bits,

@@ -98,6 +98,12 @@ typedef struct {
                                output instead.  Results are bit-identical either way.  NULL = never
                                split.  Launches that share a workspace must not overlap on the GPU. */
     long long workspace_bytes;
+    const void *prepared;   /* optional, convolutions only: this layer's weights expanded ahead of time
+                               by ds_conv2d_prepare for exactly this geometry (B, C, H, W, OC, window,
+                               stride, padding, bits, base).  With it the launch skips its own
+                               weight expansion (two small kernels).  NULL = expand per launch (with
+                               a workspace) or decode in the kernel (without).                     */
+    long long prepared_bytes;
 } ds_fuse_t;
 
 /*
@@ -194,6 +200,21 @@ int ds_avgpool_fix_i32(const int32_t *x, int32_t *out, int B, int C, int H, int 
  * operations per second (one op = one shift plus one signed accumulate) to *ops_per_s.
  */
 int ds_pipe_peak(int mode, int iters, double *ops_per_s, void *stream);
+
+/*
+ * Expands the packed weights of one convolution layer once, for callers whose weights do not
+ * change between calls (inference): the result goes into fuse->prepared (device memory of the
+ * caller, fuse->prepared_bytes long) and is handed to later ds_conv2d_ex calls of the SAME
+ * geometry through the same two fields.  *bytes_needed receives the size this geometry wants:
+ * 0 when its launches would not use expanded weights (few rows, integer path, few channels), in
+ * which case nothing is written and `prepared` may stay NULL.  Call with fuse->prepared = NULL
+ * to ask for the size only.  DS_ERR_SCRATCH if the buffer is too small.  The other fields of
+ * `fuse` must be the ones the later calls will use (they select the arithmetic path).  No
+ * counterpart in the reference, which decodes the packed words inside every kernel launch.
+ */
+int ds_conv2d_prepare(const int32_t *packed, int B, int C, int H, int W, int OC, int KH, int KW,
+                      int sh, int sw, int ph, int pw, int bits, int base, const ds_fuse_t *fuse,
+                      long long *bytes_needed, void *stream);
 
 /*
  * Reads and clears the device-side flag that a kernel of this library sets when one of its

@@ -386,6 +386,42 @@ def test_conv_with_and_without_workspace_agree(oracle, cuda_device, shape):
     assert (n1 - n0, n2 - n1) == (3, 1)
 
 
+def test_weights_prepared_once_are_reused(oracle, cuda_device):
+    """conv2d_fused expands a layer's weights on its first call for a geometry (ds_conv2d_prepare)
+    and hands the buffer to every later call: three kernels, then one, same bits as the oracle;
+    a geometry whose launches do not use expanded weights asks for no buffer."""
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(99)
+    B, C, H, OC = 12, 16, 28, 40
+    x = acts_q16(rng, (B, C, H, H))
+    shift, sign = weights(rng, (OC, C, 3, 3))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    ref = np.maximum(oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1)), 0)
+    lib = _ffi.lib()
+    counts = []
+    for _ in range(3):
+        n0 = lib.ds_launch_count()
+        out = kernels.conv2d_fused(_t(x, cuda_device), (OC, C, 3, 3), _t(bias, cuda_device), cw, 1, 1,
+                                   in_kind=_ffi.IN_I32_CLAMP, act_integer_bits=4, act_fraction_bits=12, relu=True)
+        counts.append(lib.ds_launch_count() - n0)
+        assert np.array_equal(out.cpu().numpy(), ref)
+    assert counts == [3, 1, 1]
+    assert len(cw._prepared) == 1 and next(iter(cw._prepared.values())) is not None
+    small = kernels.conv2d_fused(_t(x[:1], cuda_device), (OC, C, 3, 3), _t(bias, cuda_device), cw, 1, 1,
+                                 in_kind=_ffi.IN_I32_CLAMP, act_integer_bits=4, act_fraction_bits=12, relu=True)
+    assert np.array_equal(small.cpu().numpy(), ref[:1])
+    assert len(cw._prepared) == 2 and sum(v is None for v in cw._prepared.values()) == 1
+    # a buffer that is too small is refused
+    f = kernels._fuse(_ffi.IN_I32_CLAMP, _ffi.OUT_I32, 4, 12, act_bits=0, workspace=kernels.workspace(cuda_device))
+    tiny = torch.empty(64, dtype=torch.int32, device=cuda_device)
+    f.prepared, f.prepared_bytes = tiny.data_ptr(), 256
+    need = ctypes.c_longlong(0)
+    rc = lib.ds_conv2d_prepare(cw.data.data_ptr(), B, C, H, H, OC, 3, 3, 1, 1, 1, 1, cw.bits, cw.base, f,
+                               ctypes.byref(need), torch.cuda.current_stream().cuda_stream)
+    assert rc == 6 and need.value > 256
+
+
 def test_plain_c_abi_entry_points(oracle, cuda_device):
     """ds_linear_i32 / ds_conv2d_i32 called directly with raw pointers, as a foreign-language
     binding would (no fused options, no workspace)."""
