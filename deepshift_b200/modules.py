@@ -199,9 +199,14 @@ class Conv2dShift(_ConvNdShift):
             if self.dilation != (1, 1) or self.groups != 1:
                 raise RuntimeError("the shift convolution kernel supports neither dilation nor groups")
             x = input.float().contiguous()
+            in_kind = _ffi.IN_F32_CONV
+            if self.kernel_size[0] * self.kernel_size[1] >= 25:
+                # a large window reads every input value many times: quantise once, in its own pass
+                x = kernels.quantize(x, self.act_integer_bits, self.act_fraction_bits, like_conv=True)
+                in_kind = _ffi.IN_I32_CLAMP
             return kernels.conv2d_fused(x, tuple(self.shift.shape), self._bias_fixed(like_conv=True),
                                         self._packed(x.device), self.stride, padding,
-                                        in_kind=_ffi.IN_F32_CONV, out_kind=_ffi.OUT_F32,
+                                        in_kind=in_kind, out_kind=_ffi.OUT_F32,
                                         act_integer_bits=self.act_integer_bits,
                                         act_fraction_bits=self.act_fraction_bits)
         self.shift.data = ste.clamp(self.shift.data, *self.shift_range)

@@ -294,6 +294,12 @@ class IntPipeline:
                 xin = t[src]
                 in_fp32 = fp32[src]
                 if op == 'conv':
+                    if in_fp32 and L.k * L.k >= 25:
+                        # a large window reads every input value many times: quantise it once in a
+                        # pass of its own instead of inside the convolution's staging code
+                        xq = torch.empty(xin.shape, dtype=torch.int32, device=dev)
+                        self.calls.append(('quant', xin, xq))
+                        xin, in_fp32 = xq, False
                     in_kind = _ffi.IN_F32_CONV if in_fp32 else _ffi.IN_I32_CLAMP
                     B, C, H, W = xin.shape
                     OH, OW = (H + 2 * L.pad - L.k) // L.stride + 1, (W + 2 * L.pad - L.k) // L.stride + 1
@@ -365,6 +371,10 @@ class IntPipeline:
                 rc = lib.ds_linear_ex(xin.data_ptr(), cw.data.data_ptr(), self.bias[li].data_ptr(), out.data_ptr(),
                                       xin.shape[0], xin.shape[1], L.cout, cw.bits, cw.base, fuse, stream)
                 _ffi.check(rc, "linear_ex")
+            elif op == 'quant':
+                _, xin, xq = c
+                _ffi.check(lib.ds_quantize_f32(xin.data_ptr(), xq.data_ptr(), xin.numel(), _ffi.IN_F32_CONV, self.I,
+                                               self.F, stream), "quantize_f32")
             elif op == 'maxpool':
                 _, xin, k, s_, p_, out = c
                 B, C, H, W = xin.shape
