@@ -12,6 +12,16 @@ namespace ds {
 void note_launch(int n = 1);
 long long launch_count();
 
+// Index of the current CUDA device for the small per-device caches the launch code keeps
+// (function attributes are set per device); -1 when it cannot be had or is out of range.
+constexpr int kMaxDevices = 64;
+inline int device_slot()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+
 // 1.5 * 2^23: a float in [2^23, 2^24) has ulp 1, so MAGIC + a (|a| < 2^22) keeps a as a
 // two's-complement integer in its low mantissa bits.
 constexpr float kMagic = 12582912.0f;

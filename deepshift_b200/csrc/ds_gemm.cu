@@ -444,7 +444,10 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     if (p.prepare_only) return DS_OK;  // this kernel decodes the packed words itself
     auto kern = gemm_kernel<NT, TMG, TNG, TN, BKT, MODE, AM>;
     const size_t smem = sizeof(S);
-    static bool attr_done = false;  // per instantiation
+    static bool done[kMaxDevices];  // per instantiation and device
+    const int dev = device_slot();
+    if (dev < 0) return DS_ERR_CUDA;
+    bool& attr_done = done[dev];
     if (!attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
             cudaGetLastError();

@@ -8,7 +8,6 @@ namespace {
 
 __device__ int g_ws_error = 0;  // never set in a correct run
 
-constexpr int kMaxDevices = 64;
 int* g_ws_error_ptr[kMaxDevices];  // device address of the flag, looked up once per device
 
 }  // namespace

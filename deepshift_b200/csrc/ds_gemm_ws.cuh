@@ -829,21 +829,25 @@ bool ws_choose_tile(GemmParams& p, bool pre)
 
 inline int num_sms()
 {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
+    static int sms[kMaxDevices];  // per device
+    const int dev = device_slot();
+    if (dev < 0) return 148;
+    if (!sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
     }
-    return sms;
+    return sms[dev];
 }
 
 // Sets the shared-memory attribute of one kernel instantiation once and checks that it can be used.
 template <int TN, int AM, bool PRE>
 int ws_kernel_ready()
 {
-    static int attr_state = 0;  // per instantiation: 0 unknown, 1 usable, -1 not usable
+    static int states[kMaxDevices];  // per instantiation and device: 0 unknown, 1 usable, -1 not usable
+    const int dev = device_slot();
+    if (dev < 0) return DS_ERR_CUDA;
+    int& attr_state = states[dev];
     if (attr_state == 0) {
         auto kern = ws_kernel<TN, AM, PRE>;
         cudaFuncAttributes fa;

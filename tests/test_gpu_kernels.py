@@ -422,6 +422,24 @@ def test_weights_prepared_once_are_reused(oracle, cuda_device):
     assert rc == 6 and need.value > 256
 
 
+def test_second_device_in_the_same_process(oracle):
+    """One process, two GPUs: function attributes, workspaces and prepared weights are kept per
+    device (skipped on a single-GPU machine)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(5)
+    x = acts_q16(rng, (10, 16, 28, 28))
+    shift, sign = weights(rng, (40, 16, 3, 3))
+    bias = rng.integers(-2000, 2000, 40).astype(np.int32)
+    ref = np.maximum(oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1)), 0)
+    for dev in (torch.device("cuda", 0), torch.device("cuda", 1), torch.device("cuda", 0)):
+        cw = _cw(shift, sign, dev)
+        out = kernels.conv2d_fused(_t(x, dev), (40, 16, 3, 3), _t(bias, dev), cw, 1, 1, in_kind=_ffi.IN_I32_CLAMP,
+                                   act_integer_bits=4, act_fraction_bits=12, relu=True)
+        assert np.array_equal(out.cpu().numpy(), ref)
+
+
 def test_plain_c_abi_entry_points(oracle, cuda_device):
     """ds_linear_i32 / ds_conv2d_i32 called directly with raw pointers, as a foreign-language
     binding would (no fused options, no workspace)."""
