@@ -472,9 +472,14 @@ template <int AM>
 int launch_am(const GemmParams& p, bool fp, cudaStream_t st)
 {
     if (fp) {
-        // Convolutions run on the warp-specialised kernel; the linear layer (x rows are
-        // contiguous in k) stages faster with all 16 warps doing their share.
-        if (AM != AM_LINEAR) {
+        // The warp-specialised kernel takes convolutions and, through 16-byte loads along k, linear
+        // layers whose rows are whole 16-byte groups; other linear layers stay on the block kernel.
+        if (AM == AM_LINEAR) {
+            if (p.K % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 && p.N > 32) {
+                const int rc = launch_ws(p, AM_LINEAR, st);
+                if (rc != DS_ERR_UNSUPPORTED) return rc;
+            }
+        } else {
             // Few output channels: a 512 x 32 tile wastes no columns where the warp-specialised
             // kernel would compute 64.
             if (narrow_tile(p)) {

@@ -265,8 +265,8 @@ __device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
 // K with integer atomics when no epilogue is fused.
 int launch_small_linear(const GemmParams& p, cudaStream_t st);
 
-// Warp-specialised FP32-pipe convolution kernel (ds_gemm_ws.cuh).  am: AM_TABLE, AM_QUAD3 or the
-// window width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
+// Warp-specialised FP32-pipe kernel (ds_gemm_ws.cuh).  am: AM_LINEAR (K a multiple of 4 and x
+// 16-byte aligned), AM_TABLE, AM_QUAD3, AM_PAIR3 or the window width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
 // then falls back to the table mode or the integer path.  The per-width entry points are what
 // launch_ws dispatches to; they expect GemmParams::err_flag to be set.
 int launch_ws(const GemmParams& p, int am, cudaStream_t st);
@@ -277,5 +277,6 @@ int launch_ws_am7(const GemmParams& p, cudaStream_t st);
 int launch_ws_table(const GemmParams& p, cudaStream_t st);
 int launch_ws_quad3(const GemmParams& p, cudaStream_t st);
 int launch_ws_pair3(const GemmParams& p, cudaStream_t st);
+int launch_ws_linear(const GemmParams& p, cudaStream_t st);
 
 }  // namespace ds

@@ -27,6 +27,7 @@ int launch_ws(const GemmParams& p0, int am, cudaStream_t st)
     GemmParams p = p0;
     p.err_flag = g_ws_error_ptr[dev];
     switch (am) {
+        case AM_LINEAR: return launch_ws_linear(p, st);
         case AM_TABLE: return launch_ws_table(p, st);
         case AM_QUAD3: return launch_ws_quad3(p, st);
         case AM_PAIR3: return launch_ws_pair3(p, st);

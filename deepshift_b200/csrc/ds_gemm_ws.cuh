@@ -206,9 +206,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // global loads (issued one tile ahead) and their conversion into shared memory.
         constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows of the largest k-tile, row mode
         constexpr int XN = ROW ? RMAX * KW : WS_BKT;      // x values per thread per tile (conv)
-        constexpr int LIN_RP = WS_PROD / 32;              // linear: x rows per pass
-        constexpr int LIN_N = BM / LIN_RP;                // linear: x values per thread per tile
-        constexpr int XREG = CONV ? XN * PIX : LIN_N;
+        // linear: a thread owns one row of x and reads its k-tile with 16-byte loads
+        static_assert(CONV || (PIX == 1 && WS_BKT % 4 == 0), "linear staging: one row per producer thread");
+        constexpr int XREG = CONV ? XN * PIX : WS_BKT;
         int xr[XREG];
         uint32_t w_reg[EW];
         static_assert(XREG <= 32, "producer registers");
@@ -262,6 +262,15 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                         // address of (b, 0, ih0, iw0): may lie outside the tensor, only valid taps are read
                         x_pix[q] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iw0) * 4;
                     }
+                }
+            } else {
+                // x is [M,K]: this thread's row
+                const int m = w.m0 + pt;
+                x_pix[0] = reinterpret_cast<const char*>(p.x);
+                rowmask[0] = colmask[0] = 0;
+                if (m < p.M) {
+                    rowmask[0] = 1u;
+                    x_pix[0] += (long long)m * p.K * 4;
                 }
             }
         };
@@ -375,17 +384,18 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     }
                 }
             } else {
-                // x is [M,K]: lanes run along k (32 wide), LIN_RP rows per pass
-                const int kl = pt & 31;
-                const int k = tile * p.bk + kl;
-                const bool kval = kl < p.bk && k < p.K;
+                // x is [M,K] with K a multiple of 4 and 16-byte aligned rows (checked by the host):
+                // whole 16-byte groups of this thread's row, each inside K or beyond it
+                const int k0 = tile * p.bk;
+                const int4* rp = reinterpret_cast<const int4*>(x_pix[0] + (long long)k0 * 4);
 #pragma unroll
-                for (int u = 0; u < LIN_N; ++u) {
-                    const int ml = LIN_RP * u + (pt >> 5);
-                    int val = padv;
-                    if (kval && m0 + ml < p.M)
-                        val = __ldg(static_cast<const int32_t*>(p.x) + ((long long)(m0 + ml) * p.K + k));
-                    xr[u] = val;
+                for (int v = 0; v < WS_BKT / 4; ++v) {
+                    int4 c = make_int4(padv, padv, padv, padv);
+                    if (rowmask[0] && 4 * v < p.bk && k0 + 4 * v < p.K) c = __ldg(rp + v);
+                    xr[4 * v + 0] = c.x;
+                    xr[4 * v + 1] = c.y;
+                    xr[4 * v + 2] = c.z;
+                    xr[4 * v + 3] = c.w;
                 }
             }
         };
@@ -454,13 +464,13 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     }
                 }
             } else {
-                const int kl = pt & 31;
-                if (kl < WS_BKT) {
+                // consecutive threads hold consecutive rows: conflict-free stores
 #pragma unroll
-                    for (int u = 0; u < LIN_N; ++u) {
+                for (int u = 0; u < WS_BKT; ++u) {
+                    if (u < p.bk) {
                         float o = operand_of<true, INK>(p, xr[u]);
-                        if (LAST && k0 + kl >= p.K) o = 0.f;
-                        s.a[st][kl][LIN_RP * u + (pt >> 5)] = o;
+                        if (LAST && k0 + u >= p.K) o = 0.f;
+                        s.a[st][u][pt] = o;
                     }
                 }
             }
@@ -791,13 +801,15 @@ template <int AM>
 bool ws_choose_tile(GemmParams& p, bool pre)
 {
     constexpr int KW = (AM == AM_QUAD3 || AM == AM_PAIR3) ? 3 : (AM >= 1 ? AM : 1);
-    constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : (AM == AM_TABLE ? 4 : 1);
+    constexpr bool LIN = AM == AM_LINEAR;  // staged in 16-byte groups of four k
+    constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : 4;
     constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows the producers have registers for
     int best = 0;
-    if (pre && AM >= 1) {
+    if (pre && (AM >= 1 || LIN)) {
         long long best_padded = 0;
         for (int rows = RMAX; rows >= 1; --rows) {
             const int bk = rows * KW;
+            if (LIN && bk % 4 != 0) continue;
             if (bk > WS_BKT || (bk < 12 && best)) continue;
             const long long padded = ((long long)p.K + bk - 1) / bk * bk;
             if (!best || padded < best_padded) {

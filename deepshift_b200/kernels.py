@@ -95,11 +95,13 @@ def linear(input, shift, sign, bias=None, conc_weight=None, use_cuda=True, act_b
     M, K = input.shape
     N = shift.size(0)
     out = torch.empty([M, N], dtype=torch.int32, device=input.device)
+    # ds_linear_i32 plus the workspace (expanded weights, shared tiles when few tiles fill the SMs)
+    f = _fuse(act_bits=act_bits, workspace=workspace(input.device) if M > 64 else None)
     with torch.cuda.device(input.device):
-        rc = _ffi.lib().ds_linear_i32(input.data_ptr(), conc_weight.data.data_ptr(),
-                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                                      M, K, N, conc_weight.bits, conc_weight.base, int(act_bits),
-                                      _stream_ptr(input.device))
+        rc = _ffi.lib().ds_linear_ex(input.data_ptr(), conc_weight.data.data_ptr(),
+                                     bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                     M, K, N, conc_weight.bits, conc_weight.base, f,
+                                     _stream_ptr(input.device))
     _ffi.check(rc, "linear")
     return out
 
@@ -166,7 +168,8 @@ def linear_fused(input, out_features, bias_i32, conc_weight, *, in_kind=_ffi.IN_
     if out is None:
         out = torch.empty([M, out_features], device=input.device,
                           dtype=torch.int32 if out_kind == _ffi.OUT_I32 else torch.float32)
-    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32)
+    f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32,
+              workspace(input.device) if M > 64 else None)
     with torch.cuda.device(input.device):
         rc = _ffi.lib().ds_linear_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias_i32.data_ptr() if bias_i32 is not None else None, out.data_ptr(),

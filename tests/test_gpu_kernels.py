@@ -81,6 +81,70 @@ def test_linear_every_field_width(oracle, cuda_device, lo, zeros, act_bits):
     assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, None))
 
 
+# Linear layers whose rows are whole 16-byte groups (K % 4 == 0) and more than 32 columns run on
+# the warp-specialised kernel: a producer thread per row of x, 16-byte loads along k.
+WS_LINEAR_SHAPES = [(65, 4, 33),        # one k-group, one ragged tile
+                    (300, 512, 200),    # producers decode the packed words (few row tiles)
+                    (2304, 260, 130),   # nine row tiles: weights expanded once per launch, ragged last k-tile
+                    (1024, 2048, 96),   # four tiles on 148 SMs: every tile is shared along K through the workspace
+                    (2100, 1000, 64),   # 256 x 64 tile
+                    (257, 36, 129)]
+
+
+@pytest.mark.parametrize("M,K,N", WS_LINEAR_SHAPES)
+def test_linear_on_warp_specialised_kernel(oracle, cuda_device, M, K, N):
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(M + K * 5 + N * 11)
+    x = acts_q16(rng, (M, K))
+    shift, sign = weights(rng, (N, K))
+    bias = rng.integers(-2000, 2000, N).astype(np.int32)
+    ref = oracle.linear(x, shift, sign, bias)
+    xt, bt, cw = _t(x, cuda_device), _t(bias, cuda_device), _cw(shift, sign, cuda_device)
+    for _ in range(2):  # the second launch finds the arrival counters as the first left them
+        out = kernels.linear(xt, _t(shift, cuda_device), None, bt, cw, act_bits=16)
+        assert np.array_equal(out.cpu().numpy(), ref)
+    assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
+    # the same layer without a workspace (plain C entry point) and on the exact integer path
+    for act_bits in (16, 0):
+        out2 = torch.empty_like(out)
+        rc = _ffi.lib().ds_linear_i32(xt.data_ptr(), cw.data.data_ptr(), bt.data_ptr(), out2.data_ptr(), M, K, N,
+                                      cw.bits, cw.base, act_bits, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        assert np.array_equal(out2.cpu().numpy(), ref)
+    flag = ctypes.c_int(-1)
+    assert _ffi.lib().ds_last_kernel_error(ctypes.byref(flag)) == 0 and flag.value == 0
+
+
+@pytest.mark.parametrize("lo,zeros", [(-1, False), (-3, False), (-7, False), (-15, False), (-31, True), (-15, True)])
+@pytest.mark.parametrize("M", [200, 2200])
+def test_linear_on_warp_specialised_kernel_every_field_width(oracle, cuda_device, lo, zeros, M):
+    """16, 10, 8, 6, 5 and 4 weights per word: k-tiles of 16, 20, 24, 24, 20 and 28 when the
+    producers decode (M = 200), the k-tile that pads K least with expanded weights (M = 2200)."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(-lo * 17 + M)
+    K, N = 204, 70
+    x = acts_q16(rng, (M, K))
+    shift, sign = weights(rng, (N, K), lo, zeros)
+    out = kernels.linear(_t(x, cuda_device), _t(shift, cuda_device), None, None, _cw(shift, sign, cuda_device),
+                         act_bits=16)
+    assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, None))
+
+
+def test_linear_unaligned_rows_stay_on_the_block_kernel(oracle, cuda_device):
+    """A view whose first row does not start on a 16-byte boundary."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(41)
+    M, K, N = 300, 64, 48
+    x = acts_q16(rng, (M, K))
+    shift, sign = weights(rng, (N, K))
+    buf = torch.zeros(M * K + 1, dtype=torch.int32, device=cuda_device)
+    xt = buf[1:].view(M, K)
+    xt.copy_(_t(x, cuda_device))
+    assert xt.data_ptr() % 16 != 0
+    out = kernels.linear(xt, _t(shift, cuda_device), None, None, _cw(shift, sign, cuda_device), act_bits=16)
+    assert np.array_equal(out.cpu().numpy(), oracle.linear(x, shift, sign, None))
+
+
 def test_linear_golden_vectors_of_the_reference(oracle, cuda_device, golden_dir):
     from deepshift_b200 import kernels
     g = np.load(os.path.join(golden_dir, "linear_ref.npz"))
