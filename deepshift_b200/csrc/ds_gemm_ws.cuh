@@ -8,7 +8,9 @@
 //     global memory before the epilogue and never wait on another consumer warp.
 //   * 8 producer warps (256 threads) gather x (implicit im2col, zero padding by predication,
 //     int32 -> x + 0.5 conversion or the fused fp32 quantiser), fetch the packed weight words
-//     and decode them through the lookup table, one k-tile ahead of the consumers.
+//     and decode them through the lookup table, one k-tile ahead of the consumers.  For a
+//     linear layer (x is [M,K]) a producer thread owns one row and reads its k-tile with
+//     16-byte loads; its stores into the k-major stage are conflict-free.
 //   * The two groups meet only at mbarriers: full[s] (one arrival per producer warp) and empty[s]
 //     (one per consumer warp) for each of the two stages.  Global-load latency, the decode chains
 //     and the stores of a stage all overlap the FFMA stream of the previous stage, so the
@@ -30,15 +32,15 @@ constexpr int WS_BKT = 28;     // largest k-tile
 constexpr int WS_STAGES = 2;
 // Register split after the roles part.  The CTA starts with 768 * 80 registers; what the
 // producers give back is all the consumers can take: a larger request would wait for registers
-// that never come.  Usual split 56 / 88 (256 * 24 >= 512 * 8).  The four-pixel staging mode needs
-// fewer producer registers, so its split is 48 / 96 (256 * 32 = 512 * 16): with 96 registers the
+// that never come.  Usual split 56 / 88 (256 * 24 >= 512 * 8).  The four-pixel staging mode and
+// the linear layer need fewer producer registers, so their split is 48 / 96 (256 * 32 = 512 * 16): with 96 registers the
 // compiler has room to fetch the next fragments early, and a consumer warp running without its
 // neighbours (which wait at the hand-shake) keeps the FMA pipe busier.
 constexpr int WS_LAUNCH_REGS = 80;
 template <int AM>
 struct WsRegs {
-    static constexpr int PROD = (AM == AM_QUAD3) ? 48 : 56;
-    static constexpr int CONS = (AM == AM_QUAD3) ? 96 : 88;
+    static constexpr int PROD = (AM == AM_QUAD3 || AM == AM_LINEAR) ? 48 : 56;
+    static constexpr int CONS = (AM == AM_QUAD3 || AM == AM_LINEAR) ? 96 : 88;
     static_assert(WS_CONS * (CONS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - PROD), "register pool");
 };
 constexpr int WS_WAIT_LIMIT = 1 << 12;  // rounds of one mbarrier wait before giving up
@@ -811,7 +813,10 @@ bool ws_choose_tile(GemmParams& p, bool pre)
             const int bk = rows * KW;
             if (LIN && bk % 4 != 0) continue;
             if (bk > WS_BKT || (bk < 12 && best)) continue;
-            const long long padded = ((long long)p.K + bk - 1) / bk * bk;
+            long long padded = ((long long)p.K + bk - 1) / bk * bk;
+            // Linear layers have long K: there the fixed cost of a k-tile (hand-shake, loop set-up;
+            // measured at about four k-steps) decides between tiles that pad K about equally.
+            if (LIN) padded = padded / bk * (bk + 4);
             if (!best || padded < best_padded) {
                 best = bk;
                 best_padded = padded;
