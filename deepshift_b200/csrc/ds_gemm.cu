@@ -517,7 +517,15 @@ int launch_conv(const GemmParams& p, bool fp, cudaStream_t st)
             rc = launch_am<3>(p, fp, st);
             break;
         case 5: rc = launch_am<5>(p, fp, st); break;
-        case 7: rc = launch_am<7>(p, fp, st); break;
+        case 7:
+            // stride 2 and padding 3 along W, rows of whole 32-byte groups: four output pixels per thread
+            if (fp && !narrow_tile(p) && p.sw == 2 && p.pw == 3 && p.W % 8 == 0 && p.OW * 2 == p.W &&
+                (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0) {
+                rc = launch_ws(p, AM_S2K7, st);
+                if (rc != DS_ERR_UNSUPPORTED) break;
+            }
+            rc = launch_am<7>(p, fp, st);
+            break;
         default: break;
     }
     if (rc == DS_ERR_UNSUPPORTED) rc = launch_am<AM_TABLE>(p, fp, st);

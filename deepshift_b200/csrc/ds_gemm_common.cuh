@@ -17,6 +17,11 @@ constexpr int AM_LINEAR = -1, AM_TABLE = 0;  // AM >= 1: row mode with KW = AM
 constexpr int AM_QUAD3 = 13;
 // The same for W a multiple of 2 only and x 8-byte aligned: two pixels per 8-byte load.
 constexpr int AM_PAIR3 = 23;
+// Row mode for 7-wide windows with stride 2 and padding 3 along W (the stem of the ImageNet
+// ResNets), W a multiple of 8 and x 16-byte aligned: a producer thread fetches the sixteen input
+// values under four neighbouring output pixels with four 16-byte loads and stores the seven
+// window columns as 16-byte vectors.
+constexpr int AM_S2K7 = 27;
 
 struct GemmParams {
     const void* x;        // int32 or fp32
@@ -266,7 +271,7 @@ __device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
 int launch_small_linear(const GemmParams& p, cudaStream_t st);
 
 // Warp-specialised FP32-pipe kernel (ds_gemm_ws.cuh).  am: AM_LINEAR (K a multiple of 4 and x
-// 16-byte aligned), AM_TABLE, AM_QUAD3, AM_PAIR3 or the window width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
+// 16-byte aligned), AM_TABLE, AM_QUAD3, AM_PAIR3, AM_S2K7 or the window width of the row mode (1, 3, 5, 7).  Returns DS_ERR_UNSUPPORTED when no k-tile fits; the caller
 // then falls back to the table mode or the integer path.  The per-width entry points are what
 // launch_ws dispatches to; they expect GemmParams::err_flag to be set.
 int launch_ws(const GemmParams& p, int am, cudaStream_t st);
@@ -278,5 +283,6 @@ int launch_ws_table(const GemmParams& p, cudaStream_t st);
 int launch_ws_quad3(const GemmParams& p, cudaStream_t st);
 int launch_ws_pair3(const GemmParams& p, cudaStream_t st);
 int launch_ws_linear(const GemmParams& p, cudaStream_t st);
+int launch_ws_s2k7(const GemmParams& p, cudaStream_t st);
 
 }  // namespace ds

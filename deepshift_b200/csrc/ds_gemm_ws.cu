@@ -31,6 +31,7 @@ int launch_ws(const GemmParams& p0, int am, cudaStream_t st)
         case AM_TABLE: return launch_ws_table(p, st);
         case AM_QUAD3: return launch_ws_quad3(p, st);
         case AM_PAIR3: return launch_ws_pair3(p, st);
+        case AM_S2K7: return launch_ws_s2k7(p, st);
         case 1: return launch_ws_am1(p, st);
         case 3: return launch_ws_am3(p, st);
         case 5: return launch_ws_am5(p, st);

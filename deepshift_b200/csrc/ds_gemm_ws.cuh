@@ -39,8 +39,8 @@ constexpr int WS_STAGES = 2;
 constexpr int WS_LAUNCH_REGS = 80;
 template <int AM>
 struct WsRegs {
-    static constexpr int PROD = (AM == AM_QUAD3 || AM == AM_LINEAR) ? 48 : 56;
-    static constexpr int CONS = (AM == AM_QUAD3 || AM == AM_LINEAR) ? 96 : 88;
+    static constexpr int PROD = (AM == AM_QUAD3 || AM == AM_LINEAR || AM == AM_S2K7) ? 48 : 56;
+    static constexpr int CONS = (AM == AM_QUAD3 || AM == AM_LINEAR || AM == AM_S2K7) ? 96 : 88;
     static_assert(WS_CONS * (CONS - WS_LAUNCH_REGS) <= WS_PROD * (WS_LAUNCH_REGS - PROD), "register pool");
 };
 constexpr int WS_WAIT_LIMIT = 1 << 12;  // rounds of one mbarrier wait before giving up
@@ -164,8 +164,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     constexpr bool CONV = AM != AM_LINEAR;
     constexpr bool QUAD = AM == AM_QUAD3;
     constexpr bool PAIR = AM == AM_PAIR3;
+    constexpr bool S2K7 = AM == AM_S2K7;
     constexpr bool ROW = AM >= 1;
-    constexpr int KW = (QUAD || PAIR) ? 3 : (ROW ? AM : 1);
+    constexpr int KW = (QUAD || PAIR) ? 3 : (S2K7 ? 7 : (ROW ? AM : 1));
     constexpr int BM = WS_BM, BN = S::BN;
     constexpr int TMG = 32, TNG = 16;
     static_assert(offsetof(S, b) % 16 == 0 && offsetof(S, ktab) % 16 == 0 && offsetof(S, full) % 8 == 0, "alignment");
@@ -232,6 +233,22 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     colmask[0] = (ow > 0 ? 1u : 0u) | (ow + 4 < p.W ? 2u : 0u);  // value left / right of the four
                     // address of (b, 0, ih0, ow): the centre tap of the first pixel
                     x_pix[0] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + ow) * 4;
+                }
+            } else if (S2K7) {
+                // this thread's four output pixels: same image, same output row, ow a multiple of 4;
+                // the sixteen inputs iw = 2*ow - 4 .. 2*ow + 11 cover their windows (iw0 = 2*ow - 3)
+                const int m = w.m0 + 4 * (pt & 63);
+                x_pix[0] = reinterpret_cast<const char*>(p.x);
+                rowmask[0] = colmask[0] = 0;
+                if (m < p.M) {
+                    const int b = m / p.P, pp = m - b * p.P;
+                    const int oh = pp / p.OW, ow = pp - oh * p.OW;
+                    const int ih0 = oh * p.sh - p.ph, iwb = 2 * ow - 4;
+                    for (int kh = 0; kh < p.KH; ++kh)
+                        if (unsigned(ih0 + kh) < unsigned(p.H)) rowmask[0] |= 1u << kh;
+                    for (int v = 0; v < 4; ++v)  // whole 16-byte groups lie inside or outside the row
+                        if (unsigned(iwb + 4 * v) < unsigned(p.W)) colmask[0] |= 1u << v;
+                    x_pix[0] += ((long long)b * p.C * p.H * p.W + (long long)ih0 * p.W + iwb) * 4;
                 }
             } else if (PAIR) {
                 // this thread's two pixels: same image, same output row, ow even
@@ -339,6 +356,20 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     xr[6 * j + 4] = c.w;
                     xr[6 * j + 5] = r;
                 }
+            } else if (S2K7) {
+                // thread = (four output pixels, row pt / 64 of the k-tile)
+                const int2 e = *reinterpret_cast<const int2*>(&s.ktab[tb][pt >> 6]);
+                const int4* rowp = reinterpret_cast<const int4*>(x_pix[0] + e.x);
+                const bool rv = (rowmask[0] >> e.y) & 1u;  // rows past the tile: kh = 31
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    int4 c = make_int4(padv, padv, padv, padv);
+                    if (rv && ((colmask[0] >> v) & 1u)) c = __ldg(rowp + v);
+                    xr[4 * v + 0] = c.x;
+                    xr[4 * v + 1] = c.y;
+                    xr[4 * v + 2] = c.z;
+                    xr[4 * v + 3] = c.w;
+                }
             } else if (PAIR) {
                 // thread = (two pixels, row group): rows rg, rg + 2, rg + 4, rg + 6 of the k-tile
 #pragma unroll
@@ -421,6 +452,20 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                             if (LAST && k0 + u * 3 + kw >= p.K) v = make_float4(0.f, 0.f, 0.f, 0.f);
                             *reinterpret_cast<float4*>(&s.a[st][u * 3 + kw][4 * (pt & 63)]) = v;
                         }
+                    }
+                }
+            } else if (S2K7) {
+                const int u = pt >> 6;
+                if (u < p.rows_per_tile) {
+                    float f[16];
+#pragma unroll
+                    for (int i = 1; i < 14; ++i) f[i] = operand_of<true, INK>(p, xr[i]);
+#pragma unroll
+                    for (int kw = 0; kw < 7; ++kw) {
+                        // pixel i of the four reads input 2*i + kw - 3, i.e. slot 2*i + kw + 1 of the sixteen
+                        float4 v = make_float4(f[kw + 1], f[kw + 3], f[kw + 5], f[kw + 7]);
+                        if (LAST && k0 + u * 7 + kw >= p.K) v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        *reinterpret_cast<float4*>(&s.a[st][u * 7 + kw][4 * (pt & 63)]) = v;
                     }
                 }
             } else if (PAIR) {
@@ -802,7 +847,7 @@ __global__ void __launch_bounds__(1024) negative_prefix_kernel(const int* __rest
 template <int AM>
 bool ws_choose_tile(GemmParams& p, bool pre)
 {
-    constexpr int KW = (AM == AM_QUAD3 || AM == AM_PAIR3) ? 3 : (AM >= 1 ? AM : 1);
+    constexpr int KW = (AM == AM_QUAD3 || AM == AM_PAIR3) ? 3 : (AM == AM_S2K7 ? 7 : (AM >= 1 ? AM : 1));
     constexpr bool LIN = AM == AM_LINEAR;  // staged in 16-byte groups of four k
     constexpr int GRAN = AM >= 1 ? KW * ((KW == 1 || KW == 3) ? 4 : 2) : 4;
     constexpr int RMAX = (KW == 1) ? 28 : (KW == 3 ? 8 : 4);  // rows the producers have registers for

@@ -202,6 +202,9 @@ CONV_CASES = [  # B, C, H, W, OC, KH, KW, stride, pad, zeros
     (2, 5, 9, 11, 7, 2, 4, (1, 2), (1, 0), True), (1, 3, 6, 6, 3, 6, 6, (1, 1), (0, 0), True),
     (2, 20, 12, 12, 50, 5, 5, (1, 1), (0, 0), True), (300, 2, 5, 5, 3, 3, 3, (1, 1), (1, 1), True),
     (2, 3, 13, 13, 8, 9, 9, (2, 2), (4, 4), True),
+    # 7x7 stride 2 padding 3 on widths that are multiples of 8: four output pixels per producer thread
+    (2, 3, 32, 32, 64, 7, 7, (2, 2), (3, 3), True), (3, 4, 22, 40, 70, 7, 7, (2, 2), (3, 3), True),
+    (2, 2, 9, 16, 5, 7, 7, (3, 2), (1, 3), True), (1, 3, 8, 8, 9, 7, 7, (2, 2), (3, 3), True),
 ]
 
 
@@ -251,7 +254,8 @@ def test_conv_rejects_dilation_and_groups(cuda_device):
 
 
 # ----------------------------------------------------------------------------------------- fused forms
-@pytest.mark.parametrize("shape", [(2, 8, 12, 12, 16, 3, 1, 1), (3, 16, 9, 9, 140, 3, 2, 1), (2, 6, 10, 10, 70, 1, 1, 0)])
+@pytest.mark.parametrize("shape", [(2, 8, 12, 12, 16, 3, 1, 1), (3, 16, 9, 9, 140, 3, 2, 1), (2, 6, 10, 10, 70, 1, 1, 0),
+                                   (2, 3, 24, 24, 40, 7, 2, 3)])
 def test_conv_fused_epilogues(oracle, cuda_device, shape):
     from deepshift_b200 import _ffi, kernels
     B, C, H, OC, k, s, p = shape[0], shape[1], shape[2], shape[4], shape[5], shape[6], shape[7]
@@ -420,6 +424,8 @@ def test_conv_tail_wave_is_split(oracle, cuda_device, B):
 
 @pytest.mark.parametrize("shape", [(12, 16, 28, 28, 40, 3, 1, 1),    # four-pixel staging, 37 row tiles
                                    (9, 3, 60, 60, 24, 7, 2, 3),      # 7-wide rows: k-tiles of 21 with a workspace
+                                   (9, 3, 64, 64, 24, 7, 2, 3),      # the same on a width of 8n: four-pixel stem staging
+                                   (9, 5, 48, 72, 100, 7, 2, 3),     # ... 256 x 128 tile, ragged last k-tile
                                    (11, 40, 30, 30, 96, 1, 2, 0),    # 1x1, stride 2
                                    (10, 12, 26, 30, 70, 3, 1, 1)])   # 3x3 on a width that is no multiple of 4
 def test_conv_with_and_without_workspace_agree(oracle, cuda_device, shape):
