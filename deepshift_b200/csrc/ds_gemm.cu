@@ -633,6 +633,8 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     rc = setup_common(p, bits, base, fuse, fp);
     if (rc) return rc;
     if (p.residual && (reinterpret_cast<uintptr_t>(p.residual) & 3u)) return DS_ERR_ALIGN;
+    p.prepared = nullptr;  // weights expanded ahead of time exist for convolutions only
+    p.prepared_bytes = 0;
     if (M <= 64) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
     return launch_am<AM_LINEAR>(p, fp, static_cast<cudaStream_t>(stream));
 }

@@ -129,7 +129,9 @@ int ds_conv2d_i32(const int32_t *x, const int32_t *packed, const int32_t *bias, 
                   int pw, int bits, int base, int act_bits, void *stream);
 
 /* As above with a fused prologue/epilogue.  x is int32 or fp32 per fuse->in_kind, out is
- * int32 or fp32 per fuse->out_kind. */
+ * int32 or fp32 per fuse->out_kind.  fuse->workspace serves ds_linear_ex (M > 64, FP32-pipe path,
+ * K a multiple of 4, x 16-byte aligned, N > 32) exactly as it serves convolutions; fuse->prepared
+ * is ignored by ds_linear_ex. */
 int ds_linear_ex(const void *x, const int32_t *packed, const int32_t *bias, void *out, int M,
                  int K, int N, int bits, int base, const ds_fuse_t *fuse, void *stream);
 int ds_conv2d_ex(const void *x, const int32_t *packed, const int32_t *bias, void *out, int B,
