@@ -43,6 +43,16 @@ def round_power_of_2(x, rounding='deterministic'):
     return (2.0 ** shift) * sign
 
 
+def clampabs(input, min, max):
+    """utils.py:44-52: |x| clamped into [min, max] in place, zeros left alone."""
+    assert min >= 0 and max >= 0
+    input[input > max] = max
+    input[input < -max] = -max
+    input[(input > 0) & (input < min)] = min
+    input[(input < 0) & (input > -min)] = -min
+    return input
+
+
 class ConcWeight():
     """utils.py:54-58: packed weights, the (non-positive) shift base and the field width."""
 

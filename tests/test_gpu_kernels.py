@@ -369,6 +369,67 @@ def test_convert_to_shift_use_kernel_end_to_end(oracle, cuda_device):
     assert np.array_equal(y, oracle.from_fixed(li, F))
 
 
+@pytest.mark.parametrize("I,F", [(4, 12), (8, 16)])
+def test_q_modules_use_kernel_match_oracle(oracle, cuda_device, I, F):
+    """DeepShift-Q layers: weights rounded to powers of two on the fly, then the same kernels.
+    (4, 12) takes the FP32-pipe path, (8, 16) the exact integer path."""
+    from deepshift_b200 import modules_q, utils
+    torch.manual_seed(17 + I)
+    rng = np.random.default_rng(I)
+    conv = modules_q.Conv2dShiftQ(6, 40, 3, stride=1, padding=1, use_kernel=True, act_integer_bits=I,
+                                  act_fraction_bits=F).to(cuda_device)
+    conv.weight.data.mul_(torch.from_numpy(rng.choice([1.0, 0.02, 30.0], conv.weight.shape).astype(np.float32)).to(cuda_device))
+    conv.weight.data[0, 0] = 0.0
+    xf = (rng.normal(0, 3, (3, 6, 10, 12))).astype(np.float32)
+    y = conv(_t(xf, cuda_device))
+    w = conv.weight.data.cpu()
+    assert float(w.abs().max()) <= 1.0 and float(w[w != 0].abs().min()) >= 2.0 ** -15
+    shift, sign = utils.get_shift_and_sign(w)
+    shift = torch.where(sign == 0, torch.zeros_like(shift), shift)   # log2(0): any value, the sign is 0
+    bias_i = (utils.round_to_fixed(conv.bias.data.cpu(), I, F) * 2 ** F).int().numpy()
+    xi = oracle.to_fixed_conv(xf, I, F)
+    ref = oracle.conv2d(xi, shift.numpy().astype(np.int32), sign.numpy().astype(np.int32), bias_i, (1, 1), (1, 1))
+    assert np.array_equal(y.cpu().numpy(), oracle.from_fixed(ref, F))
+    assert conv(_t(xf, cuda_device)).equal(y)            # packed weights are cached
+    conv.weight.data.neg_()                               # same storage, no version bump: repack on request
+    conv.conc_weight = None
+    assert np.array_equal(conv(_t(xf, cuda_device)).cpu().numpy(),
+                          oracle.from_fixed(oracle.conv2d(xi, shift.numpy().astype(np.int32),
+                                                          -sign.numpy().astype(np.int32), bias_i, (1, 1), (1, 1)), F))
+
+    lin = modules_q.LinearShiftQ(52, 70, use_kernel=True, act_integer_bits=I, act_fraction_bits=F).to(cuda_device)
+    xl = rng.normal(0, 2, (5, 13, 52)).astype(np.float32)   # 65 rows after flattening
+    yl = lin(_t(xl, cuda_device))
+    assert tuple(yl.shape) == (5, 13, 70)
+    wl = lin.weight.data.cpu()
+    shift, sign = utils.get_shift_and_sign(wl)
+    bias_i = (utils.round_to_fixed(lin.bias.data.cpu(), I, F) * 2 ** F).int().numpy()
+    xi = oracle.to_fixed_conv(xl.reshape(-1, 52), I, F)
+    ref = oracle.linear(xi, shift.numpy().astype(np.int32), sign.numpy().astype(np.int32), bias_i)
+    assert np.array_equal(yl.cpu().numpy().reshape(-1, 70), oracle.from_fixed(ref, F))
+
+
+def test_convert_to_shift_q_use_kernel_end_to_end(cuda_device):
+    """A converted DeepShift-Q model with use_kernel=True agrees with its own fp32 path up to the
+    truncation of the right shifts: at most one unit of 2^-F per term."""
+    import torch.nn as nn
+    from deepshift_b200 import convert
+    torch.manual_seed(23)
+    I, F = 4, 12
+    model = nn.Sequential(nn.Conv2d(3, 16, 3, padding=1), nn.ReLU(), nn.Conv2d(16, 8, 3, stride=2, padding=1), nn.ReLU(),
+                          nn.Flatten(), nn.Linear(8 * 16, 10)).to(cuda_device)
+    model, n = convert.convert_to_shift(model, 10, 'Q', use_kernel=True, act_integer_bits=I, act_fraction_bits=F)
+    assert n == 2
+    x = torch.randn(70, 3, 8, 8, device=cuda_device)
+    y = model(x)
+    for m in model:
+        if hasattr(m, 'use_kernel'):
+            m.use_kernel = False
+    y_float = model(x)
+    assert y.shape == y_float.shape == (70, 10)
+    assert float((y - y_float).detach().abs().max()) < 0.2
+
+
 def test_no_kernel_wait_ran_out(cuda_device):
     """The warp-specialised kernel's bounded waits never give up in a correct run."""
     from deepshift_b200 import _ffi

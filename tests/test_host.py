@@ -72,8 +72,6 @@ def test_convert_to_shift_structure_and_count():
     m2 = nn.Sequential(nn.Conv2d(3, 8, 3), nn.Conv2d(8, 8, 3))
     m2, n = convert.convert_to_shift(m2, 1, 'PS')
     assert n == 1 and type(m2[1]) is modules.Conv2dShift and type(m2[0]) is nn.Conv2d
-    with pytest.raises(NotImplementedError):
-        convert.convert_to_shift(nn.Sequential(nn.Linear(2, 2)), 1, 'Q')
     with pytest.raises(ValueError):
         convert.convert_to_shift(nn.Sequential(nn.Linear(2, 2)), 1, 'XYZ')
 
@@ -120,6 +118,68 @@ def test_kernel_mode_without_cuda_raises():
         from deepshift_b200.utils import ConcWeight
         kernels.linear(torch.zeros(1, 4, dtype=torch.int32), torch.zeros(2, 4), None, None,
                        ConcWeight(torch.zeros(2, dtype=torch.int32), 0, 3))
+
+
+# --------------------------------------------------------------------------- DeepShift-Q modules
+def test_q_module_signatures_and_attributes_match_reference():
+    import inspect
+    from deepshift_b200 import modules_q
+    lin = inspect.signature(modules_q.LinearShiftQ.__init__)
+    assert list(lin.parameters)[1:] == ['in_features', 'out_features', 'bias', 'check_grad', 'use_kernel', 'use_cuda',
+                                        'rounding', 'weight_bits', 'act_integer_bits', 'act_fraction_bits']
+    conv = inspect.signature(modules_q.Conv2dShiftQ.__init__)
+    assert list(conv.parameters)[1:] == ['in_channels', 'out_channels', 'kernel_size', 'stride', 'padding', 'dilation',
+                                         'groups', 'bias', 'padding_mode', 'check_grad', 'use_kernel', 'use_cuda',
+                                         'rounding', 'weight_bits', 'act_integer_bits', 'act_fraction_bits']
+    m = modules_q.Conv2dShiftQ(3, 4, 3, weight_bits=5)
+    assert m.shift_range == (-15, 0) and m.conc_weight is None and tuple(m.weight.shape) == (4, 3, 3, 3)
+    assert modules_q.LinearShiftQ(5, 2, weight_bits=4).shift_range == (-7, 0)
+
+
+def test_q_float_path_uses_clamped_power_of_two_weights():
+    from deepshift_b200 import modules_q, utils
+    torch.manual_seed(5)
+    conv = modules_q.Conv2dShiftQ(3, 4, 3, padding=1, act_integer_bits=4, act_fraction_bits=12)
+    conv.weight.data[0, 0, 0, 0] = 3.0       # clamped to 1
+    conv.weight.data[0, 0, 0, 1] = -1e-9     # clamped to -2^-15
+    conv.weight.data[0, 0, 0, 2] = 0.0       # stays 0
+    x = torch.randn(2, 3, 5, 5) * 3
+    y = conv(x)
+    w = conv.weight.data
+    assert w[0, 0, 0, 0] == 1.0 and w[0, 0, 0, 1] == -2.0 ** -15 and w[0, 0, 0, 2] == 0.0
+    wq = utils.round_power_of_2(w)
+    ref = torch.nn.functional.conv2d(utils.round_to_fixed(x, 4, 12), wq, utils.round_to_fixed(conv.bias.data, 4, 12),
+                                     padding=1)
+    assert torch.equal(y, ref)
+    lin = modules_q.LinearShiftQ(6, 3, act_integer_bits=4, act_fraction_bits=12)
+    xl = torch.randn(4, 6)
+    refl = utils.round_to_fixed(xl, 4, 12).mm(utils.round_power_of_2(lin.weight.data).t()) + lin.bias.data
+    assert torch.allclose(lin(xl), refl, atol=0, rtol=0)
+
+
+def test_convert_to_shift_q_and_round_shift_weights():
+    from deepshift_b200 import convert, modules_q
+    torch.manual_seed(6)
+    model = nn.Sequential(nn.Conv2d(3, 8, 3, padding=1), nn.ReLU(), nn.Flatten(), nn.Linear(8 * 36, 10))
+    w0 = model[0].weight
+    model, n = convert.convert_to_shift(model, 10, 'Q', act_integer_bits=4, act_fraction_bits=12)
+    assert n == 1 and type(model[0]) is modules_q.Conv2dShiftQ and type(model[3]) is modules_q.LinearShiftQ
+    assert model[0].weight is w0
+    x = torch.randn(2, 3, 6, 6)
+    y = model(x)
+    rounded = convert.round_shift_weights(model, clone=True, act_integer_bits=4, act_fraction_bits=12)
+    assert torch.equal(torch.log2(rounded[0].weight.data.abs()).frac(), torch.zeros_like(rounded[0].weight.data))
+    assert torch.equal(rounded(x), y)
+    with pytest.raises(ValueError):
+        convert.convert_to_shift(nn.Sequential(nn.Linear(2, 2)), 1, 'X')
+
+
+def test_q_kernel_mode_without_cuda_raises():
+    from deepshift_b200 import modules_q
+    with pytest.raises(RuntimeError, match="no CPU kernel path"):
+        modules_q.LinearShiftQ(4, 2, use_kernel=True, use_cuda=False)(torch.zeros(1, 4))
+    with pytest.raises(RuntimeError, match="no CPU kernel path"):
+        modules_q.Conv2dShiftQ(1, 2, 3, use_kernel=True, use_cuda=False)(torch.zeros(1, 1, 4, 4))
 
 
 # --------------------------------------------------------------------------- workloads
