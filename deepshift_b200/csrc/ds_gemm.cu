@@ -548,7 +548,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     const bool in_clamp = f.in_kind == DS_IN_I32_CLAMP;
     const bool needs_if = f.in_kind != DS_IN_I32 || f.out_kind != DS_OUT_I32 || f.requant;
     if (needs_if && (F < 0 || F > 30)) return DS_ERR_BAD_ARG;
-    if ((f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp) && (I < 1 || I + F > 31)) return DS_ERR_BAD_ARG;
+    if ((f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp) && (I < 1 || I + F > 32)) return DS_ERR_BAD_ARG;
     p.in_kind = f.in_kind;
     p.out_kind = f.out_kind;
     p.relu = f.relu;

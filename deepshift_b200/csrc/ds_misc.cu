@@ -289,7 +289,7 @@ extern "C" int ds_quantize_f32(const float* x, int32_t* out, long long n, int ki
 {
     if (n < 0 || (n > 0 && (!x || !out))) return DS_ERR_BAD_ARG;
     if (kind != DS_IN_F32_CONV && kind != DS_IN_F32_LINEAR) return DS_ERR_BAD_ARG;
-    if (F < 0 || F > 30 || (kind == DS_IN_F32_CONV && (I < 1 || I + F > 31))) return DS_ERR_BAD_ARG;
+    if (F < 0 || F > 30 || (kind == DS_IN_F32_CONV && (I < 1 || I + F > 32))) return DS_ERR_BAD_ARG;
     if (n == 0) return DS_OK;
     Quant q;
     q.scale = float(1ll << F);

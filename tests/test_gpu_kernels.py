@@ -430,6 +430,28 @@ def test_convert_to_shift_q_use_kernel_end_to_end(cuda_device):
     assert float((y - y_float).detach().abs().max()) < 0.2
 
 
+def test_reference_default_activation_bits_16_16(oracle, cuda_device):
+    """The constructors' defaults, act_integer_bits = act_fraction_bits = 16: codes fill the whole
+    int32 range ([-2^31, 32767 * 2^16]) and sums wrap modulo 2^32 as in the reference."""
+    from deepshift_b200 import kernels, modules
+    rng = np.random.default_rng(1616)
+    xf = (rng.normal(0, 1, (2, 3, 9, 9)) * rng.choice([1.0, 300.0, 40000.0], (2, 3, 9, 9))).astype(np.float32)
+    xf[0, 0, 0, :4] = [-32768.0, 32767.99, 1e9, -1e9]
+    codes = kernels.quantize(_t(xf, cuda_device), 16, 16, like_conv=True)
+    xi = oracle.to_fixed_conv(xf, 16, 16)
+    assert xi.min() == -2 ** 31 and xi.max() == 32767 * 65536
+    assert np.array_equal(codes.cpu().numpy(), xi)
+    conv = modules.Conv2dShift(3, 40, 3, padding=1, use_kernel=True).to(cuda_device)   # default bits
+    shift, sign = weights(rng, (40, 3, 3, 3))
+    conv.shift.data = _t(shift.astype(np.float32), cuda_device)
+    conv.sign.data = _t(sign.astype(np.float32), cuda_device)
+    conv.bias.data = _t(rng.normal(0, 100, 40).astype(np.float32), cuda_device)
+    y = conv(_t(xf, cuda_device))
+    bias_i = oracle.to_fixed_conv(conv.bias.data.cpu().numpy(), 16, 16)
+    ref = oracle.conv2d(xi, shift, sign, bias_i, (1, 1), (1, 1))
+    assert np.array_equal(y.cpu().numpy(), oracle.from_fixed(ref, 16))
+
+
 def test_no_kernel_wait_ran_out(cuda_device):
     """The warp-specialised kernel's bounded waits never give up in a correct run."""
     from deepshift_b200 import _ffi
