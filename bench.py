@@ -28,6 +28,11 @@ import sys
 import threading
 import time
 
+# torchrun sets OMP_NUM_THREADS=1 for every rank.  The reference arm runs on rank 0 alone and is
+# meant to use every host core it may run on, so the limit is lifted before any OpenMP runtime loads.
+if "--impl" in sys.argv and "reference" in sys.argv and os.environ.get("RANK", "0") == "0":
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -118,6 +123,11 @@ def cpu_reference_images_per_s(n_images=None, max_images=16):
             return O.ref_linear(x, shift, sign, bias)
         O.conv2d, O.linear = conv2d, linear
     try:
+        if kind == "reference" and os.environ.get("RANK", "0") == "0":
+            # at::parallel_for's pool: every core this process may run on (torchrun's default is 1)
+            want = int(os.environ.get("OMP_NUM_THREADS", "0")) or torch.get_num_threads()
+            if want > torch.get_num_threads():
+                torch.set_num_threads(want)
         cores = torch.get_num_threads() if kind == "reference" else O.num_threads()
         # The reference kernels parallelise over the batch only (at::parallel_for over images), so
         # the sample holds one image per usable core, at most max_images.
