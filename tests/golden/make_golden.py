@@ -11,7 +11,8 @@ Two sources, both executed in a container where the reference checkout is mounte
 
 Inputs are seeded; each file stores inputs and the reference's outputs.
 
-Usage: python tests/golden/make_golden.py [path-to-reference-checkout]
+Usage: python tests/golden/make_golden.py [--only-q] [path-to-reference-checkout]
+(--only-q: write q_ref.npz, the DeepShift-Q module vectors, and leave the other files alone)
 """
 import os
 import sys
@@ -41,6 +42,39 @@ def acts(rng, shape, kind="q16"):
     if kind == "wide":  # unclamped linear inputs
         return rng.integers(-(1 << 27), 1 << 27, shape).astype(np.int32)
     raise ValueError(kind)
+
+
+def _import_reference(reference_root):
+    sys.path.insert(0, os.path.join(reference_root, "pytorch"))
+    # kernels.py:4-8 binds deepshift_cpu only if deepshift_cuda imports first.
+    sys.modules.setdefault("deepshift_cuda", types.ModuleType("deepshift_cuda"))
+    sys.modules["deepshift_cpu"] = O.ref_module()
+
+
+def main_q(reference_root):
+    """q_ref.npz: the reference's Conv2dShiftQ forward with use_kernel=True, use_cuda=False
+    (modules_q.py:283-300 -> 141-161 -> kernels.py:54-66 -> deepshift_cpu.convolution_kernel).
+    padding = 0, because kernels.conv2d pads only W on the CPU path (kernels.py:58), and no zero
+    weights, because convolution_kernel adds them as +1 (shift_cpu.cpp:351-353)."""
+    assert build_ref.build(reference_root) is not None, "reference checkout not found"
+    _import_reference(reference_root)
+    import deepshift.modules_q as ref_q
+    out = {}
+    rng = np.random.default_rng(4000)
+    for i, (cin, cout, k, stride, hw, scale) in enumerate([(3, 6, 3, 1, 8, 1.0), (4, 5, 5, 2, 11, 40.0),
+                                                           (2, 7, 1, 1, 6, 1e-4)]):
+        torch.manual_seed(40 + i)
+        conv = ref_q.Conv2dShiftQ(cin, cout, k, stride=stride, padding=0, bias=True, use_kernel=True,
+                                  use_cuda=False, act_integer_bits=4, act_fraction_bits=12)
+        conv.weight.data.mul_(scale)   # beyond 1 and below 2^-15: the module's clamp acts
+        xin = torch.from_numpy(rng.normal(0, 3, (2, cin, hw, hw)).astype(np.float32))
+        out[f"w{i}"], out[f"bias{i}"] = conv.weight.data.numpy().copy(), conv.bias.data.numpy().copy()
+        out[f"x{i}"], out[f"stride{i}"] = xin.numpy().copy(), np.int32(stride)
+        with torch.no_grad():
+            out[f"y{i}"] = conv(xin.clone()).numpy()
+    out["n"] = np.int32(3)
+    np.savez_compressed(os.path.join(HERE, "q_ref.npz"), **out)
+    print("q_ref.npz", os.path.getsize(os.path.join(HERE, "q_ref.npz")), "bytes")
 
 
 def main(reference_root):
@@ -85,10 +119,7 @@ def main(reference_root):
     np.savez_compressed(os.path.join(HERE, "conv_ref.npz"), **out)
 
     # ---- float glue from the reference's Python package ----------------------------------
-    sys.path.insert(0, os.path.join(reference_root, "pytorch"))
-    # kernels.py:4-8 binds deepshift_cpu only if deepshift_cuda imports first.
-    sys.modules.setdefault("deepshift_cuda", types.ModuleType("deepshift_cuda"))
-    sys.modules["deepshift_cpu"] = O.ref_module()
+    _import_reference(reference_root)
     import deepshift.modules as ref_modules
     import deepshift.utils as ref_utils
 
@@ -130,4 +161,8 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DEEPSHIFT_REFERENCE", "/root/reference"))
+    args = [a for a in sys.argv[1:] if a != "--only-q"]
+    root = args[0] if args else os.environ.get("DEEPSHIFT_REFERENCE", "/root/reference")
+    if "--only-q" not in sys.argv:
+        main(root)
+    main_q(root)

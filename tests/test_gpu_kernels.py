@@ -409,6 +409,18 @@ def test_q_modules_use_kernel_match_oracle(oracle, cuda_device, I, F):
     assert np.array_equal(yl.cpu().numpy().reshape(-1, 70), oracle.from_fixed(ref, F))
 
 
+def test_q_module_golden_forward_of_the_reference(cuda_device, golden_dir):
+    from deepshift_b200 import modules_q
+    g = np.load(os.path.join(golden_dir, "q_ref.npz"))
+    for i in range(int(g["n"])):
+        w = g[f"w{i}"]
+        conv = modules_q.Conv2dShiftQ(w.shape[1], w.shape[0], w.shape[2], stride=int(g[f"stride{i}"]), padding=0,
+                                      use_kernel=True, act_integer_bits=4, act_fraction_bits=12).to(cuda_device)
+        conv.weight.data = _t(w, cuda_device)
+        conv.bias.data = _t(g[f"bias{i}"], cuda_device)
+        assert np.array_equal(conv(_t(g[f"x{i}"], cuda_device)).cpu().numpy(), g[f"y{i}"]), i
+
+
 def test_convert_to_shift_q_use_kernel_end_to_end(cuda_device):
     """A converted DeepShift-Q model with use_kernel=True agrees with its own fp32 path up to the
     truncation of the right shifts: at most one unit of 2^-F per term."""

@@ -174,6 +174,20 @@ def test_convert_to_shift_q_and_round_shift_weights():
         convert.convert_to_shift(nn.Sequential(nn.Linear(2, 2)), 1, 'X')
 
 
+def test_q_golden_vectors_of_the_reference_match_the_oracle(oracle, golden_dir):
+    """The reference's Conv2dShiftQ forward (use_kernel=True on its CPU kernel) restated: clamp
+    |w| into [2^-15, 1], round to a power of two, quantise input and bias, integer convolution."""
+    from deepshift_b200 import utils
+    g = np.load(os.path.join(golden_dir, "q_ref.npz"))
+    for i in range(int(g["n"])):
+        w = utils.clampabs(torch.from_numpy(g[f"w{i}"].copy()), 2.0 ** -15, 1.0)
+        shift, sign = utils.get_shift_and_sign(w)
+        st = int(g[f"stride{i}"])
+        ref = oracle.conv2d(oracle.to_fixed_conv(g[f"x{i}"], 4, 12), shift.numpy().astype(np.int32),
+                            sign.numpy().astype(np.int32), oracle.to_fixed_conv(g[f"bias{i}"], 4, 12), (st, st), (0, 0))
+        assert np.array_equal(oracle.from_fixed(ref, 12), g[f"y{i}"]), i
+
+
 def test_q_kernel_mode_without_cuda_raises():
     from deepshift_b200 import modules_q
     with pytest.raises(RuntimeError, match="no CPU kernel path"):
