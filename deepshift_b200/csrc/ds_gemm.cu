@@ -578,21 +578,32 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.residual = f.residual;
     p.q.scale = float(1ll << (needs_if ? F : 0));
     p.inv_scale = 1.0f / p.q.scale;
-    p.q.sign_mode = (f.in_kind == DS_IN_F32_CONV && I == 1);
+    const bool uses_rtf = f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp;
+    const bool sign_mode = uses_rtf && I == 1;  // round_to_fixed(x, 1, F) = sign(x) - 1
+    p.q.sign_mode = sign_mode ? 1 : 0;
     p.q.lo = p.q.hi = 0.f;
-    p.rq_lo = p.rq_hi = 0;
-    if (f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp) {
+    p.rq_lo = p.rq_hi = p.rq_add = 0;
+    p.rq_mul = 1;
+    if (sign_mode) {
+        // codes {-2^(F+1), -2^F, 0} for x < 0, x == 0, x > 0
+        p.q.lo = -float(2ll << F);
+        p.rq_lo = -1;
+        p.rq_hi = 1;
+        p.rq_mul = int(1u << F);
+        p.rq_add = -p.rq_mul;
+    } else if (uses_rtf) {
         const long long lo = -(1ll << (I - 1 + F)), hi = ((1ll << (I - 1)) - 1) * (1ll << F);
         p.q.lo = float(lo);
         p.q.hi = float(hi);
         p.rq_lo = int(lo);
         p.rq_hi = int(hi);
     }
+    p.in_mul2 = int(2u * unsigned(p.rq_mul));
+    p.in_add2 = int(2u * unsigned(p.rq_add) + unsigned(kHalfMagicBits + 1));
     // FP32-pipe path: needs base == 0, every |x| <= 2^(act_bits-1) <= 2^17, and room for at
     // least one k-tile of terms (each of magnitude <= 2^(act_bits-1) + 1) between drains.
     int ab = f.act_bits;
-    if (f.in_kind == DS_IN_F32_CONV) ab = p.q.sign_mode ? F + 2 : I + F;
-    if (in_clamp) ab = I + F;
+    if (f.in_kind == DS_IN_F32_CONV || in_clamp) ab = sign_mode ? F + 2 : I + F;
     if (f.in_kind == DS_IN_F32_LINEAR) ab = 0;
     use_fp = (base == 0 && ab >= 1 && ab <= 18);
     p.flush_tiles = 0;

@@ -68,7 +68,11 @@ struct GemmParams {
     int prepare_only;        // this call only fills `prepared` (or reports its size), no convolution
     long long* needed_out;   // host: receives the bytes `prepared` needs for this geometry
     Quant q;
-    int rq_lo, rq_hi;
+    // round_to_fixed on a value that already is an int32 code (DS_IN_I32_CLAMP, `requant`):
+    // code' = clamp(code, rq_lo, rq_hi) * rq_mul + rq_add.  I >= 2: the clamp alone (mul 1, add 0).
+    // I == 1 (utils.py:12-13, sign(x) - 1): clamp to [-1, 1], times 2^F, minus 2^F.
+    int rq_lo, rq_hi, rq_mul, rq_add;
+    int in_mul2, in_add2;  // FP path: float bits of 1.5*2^22 + code' + 0.5 = clamp * in_mul2 + in_add2
     float inv_scale;  // 2^-F
 };
 
@@ -119,7 +123,7 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
             v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + oidx)));
         }
         if (p.relu) v = max(v, 0);
-        if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi);
+        if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi) * p.rq_mul + p.rq_add;
         if (p.round_f32) v = __float2int_rn(__int2float_rn(v));
         return v;
     };
@@ -244,8 +248,12 @@ constexpr int INK_I32 = 0, INK_F32 = 1, INK_I32_CLAMP = 2;
 template <bool FP, int INK>
 __device__ __forceinline__ float operand_of(const GemmParams& p, int v)
 {
+    if (INK == INK_I32_CLAMP) {
+        const int c = min(max(v, p.rq_lo), p.rq_hi);
+        if (FP) return __int_as_float(c * p.in_mul2 + p.in_add2) - kHalfMagic;
+        return __int_as_float(c * p.rq_mul + p.rq_add);
+    }
     if (INK != INK_F32) {
-        if (INK == INK_I32_CLAMP) v = min(max(v, p.rq_lo), p.rq_hi);
         // x + 0.5 without an int->float conversion: adding 2x+1 to the bits of 1.5*2^22
         // (ulp 0.5) gives 1.5*2^22 + x + 0.5 exactly for |x| < 2^20.
         return FP ? (__int_as_float(2 * v + (kHalfMagicBits + 1)) - kHalfMagic) : __int_as_float(v);

@@ -90,10 +90,13 @@ __device__ __forceinline__ void warp_arrive(unsigned long long* bar)
 // suspend the thread for up to WS_WAIT_NS before it reports "not yet", so a waiting warp issues
 // almost nothing.  Returns false after WS_WAIT_LIMIT such rounds (seconds; a correct run waits
 // microseconds).
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity)
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, bool gave_up = false)
 {
     const unsigned addr = smem_u32(bar);
-    for (int i = 0; i < WS_WAIT_LIMIT; ++i) {
+    // A thread that has given up once makes its later waits short (one round), so that a launch in
+    // which something went wrong still ends within seconds instead of one full limit per wait.
+    const int limit = gave_up ? 1 : WS_WAIT_LIMIT;
+    for (int i = 0; i < limit; ++i) {
         unsigned ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -563,6 +566,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // stores -- also across item boundaries: while the consumers finish an output tile and run
         // its epilogue, the first k-tiles of the next item are already being staged.
         int item = blockIdx.x, seq = 0, git = 0;
+        bool pbad = false;
         if (item < total_items) {
             WsItem cur = ws_item(p, item, BM, BN);
             int tile = cur.t_begin;
@@ -572,7 +576,10 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             issue_loads(tile, cur.m0);
             while (true) {
                 const int st = git % WS_STAGES;
-                if (git >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u)) s.err = 1;
+                if (git >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u, pbad)) {
+                    pbad = true;
+                    s.err = 1;
+                }
                 const int k0 = tile * p.bk;
                 // Expanded weights are 0 beyond K, so the x values stored there need no care.
                 const bool last = !PRE && tile + 1 >= p.ntiles;
@@ -641,7 +648,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         int ndrains = 0, since = 0;
         for (int it = 0; it < my_tiles; ++it, ++git) {
             const int st = git % WS_STAGES;
-            if (!mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u)) bad = true;
+            if (!mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u, bad)) bad = true;
             // The k-tile sizes of 3x3, 1x1 / 7x7 and 5x5 windows get fully unrolled loops.
             auto k_loop = [&](auto bk_tag) {
                 constexpr int CBK = decltype(bk_tag)::value;
@@ -1011,7 +1018,9 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
             p.tail_tps = (p.ntiles + p.tail_splits - 1) / p.tail_splits;
             p.tail_splits = (p.ntiles + p.tail_tps - 1) / p.tail_tps;
         }
-    } else if (p.counters && !p.partials && tiles <= p.counter_slots && p.ntiles >= 16) {
+    } else if (p.counters && !p.partials && tiles <= p.counter_slots && p.ntiles >= 16 &&
+               static_cast<const void*>(p.residual) != p.out) {
+        // (an in-place residual add, residual == out, would be wiped by the zeroing below)
         // Split-K of every tile through integer atomics on the zeroed output, for callers whose
         // workspace holds counters only: used when the tiles alone fill the SMs badly.
         auto eff = [&](int sp) {

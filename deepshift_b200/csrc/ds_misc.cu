@@ -161,86 +161,6 @@ __global__ void __launch_bounds__(256) peak_kernel(int iters, int seed, int* sin
     if (r == 0x7fffffff) *sink = r;  // practically never; keeps the work alive
 }
 
-// Packed FP32 pairs: one fma.rm.f32x2 does two terms.  MODE 3: only those; MODE 4: one
-// independent integer instruction issued beside every packed FMA.
-template <int MODE>
-__global__ void __launch_bounds__(256) peak2_kernel(int iters, int seed, int* sink)
-{
-    unsigned long long w[4], f[kChains];
-    int a[kChains];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const unsigned lo = ((127u - (((seed >> (3 * j)) & 7) + 1)) << 23) | (((seed >> j) & 1) ? 0u : 0x80000000u);
-        w[j] = (unsigned long long)lo | ((unsigned long long)(lo ^ 0x80000000u) << 32);
-    }
-#pragma unroll
-    for (int c = 0; c < kChains; ++c) {
-        f[c] = (unsigned long long)__float_as_uint(kMagic + float(c)) * 0x100000001ull;
-        a[c] = seed * (threadIdx.x + 1) + c;
-    }
-    const float xv = float(threadIdx.x) + 0.5f;
-    const unsigned long long x2 = (unsigned long long)__float_as_uint(xv) * 0x100000001ull;
-    for (int it = 0; it < iters; ++it) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-#pragma unroll
-            for (int c = 0; c < kChains; ++c) {
-                asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(f[c]) : "l"(x2), "l"(w[r]));
-                if (MODE == 4) a[c] = (a[c] ^ seed) + it;
-            }
-    }
-    unsigned long long r = 0;
-#pragma unroll
-    for (int c = 0; c < kChains; ++c) r ^= f[c] + (unsigned)a[c];
-    if (r == 0x7fffffffull) *sink = int(r);
-}
-
-// Register-only outer products with the operand pattern of the GEMM inner loop.
-// MODE 5: 4 row pairs x 8 columns of packed FMAs; MODE 6: 8 x 8 scalar FMAs.
-template <int MODE>
-__global__ void __launch_bounds__(256) peak3_kernel(int iters, int seed, int* sink)
-{
-    unsigned long long a2[4], b2[8], c2[4][8];
-    float a[8], b[8], c[8][8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const unsigned wb = ((127u - ((seed >> j) & 7)) << 23) | (((seed >> (j + 3)) & 1) ? 0u : 0x80000000u);
-        b2[j] = (unsigned long long)wb * 0x100000001ull;
-        b[j] = __uint_as_float(wb);
-        a[j] = float(threadIdx.x + j) + 0.5f;
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        a2[i] = (unsigned long long)__float_as_uint(a[2 * i]) | ((unsigned long long)__float_as_uint(a[2 * i + 1]) << 32);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) c2[i][j] = (unsigned long long)unsigned(kMagicBits) * 0x100000001ull;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) c[i][j] = kMagic;
-    for (int it = 0; it < iters; ++it) {
-        if (MODE == 5) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    asm volatile("fma.rm.f32x2 %0, %1, %2, %0;" : "+l"(c2[i][j]) : "l"(a2[i]), "l"(b2[j]));
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) c[i][j] = __fmaf_rd(a[i], b[j], c[i][j]);
-        }
-    }
-    unsigned long long r = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) r ^= (MODE == 5) ? c2[i / 2][j] : (unsigned long long)__float_as_uint(c[i][j]);
-    if (r == 0x7fffffffull) *sink = int(r);
-}
-
 }  // namespace
 
 static std::atomic<long long> g_launches{0};
@@ -352,7 +272,7 @@ extern "C" int ds_avgpool_fix_i32(const int32_t* x, int32_t* out, int B, int C, 
 
 extern "C" int ds_pipe_peak(int mode, int iters, double* ops_per_s, void* stream)
 {
-    if (!ops_per_s || iters <= 0 || mode < 0 || mode > 6) return DS_ERR_BAD_ARG;
+    if (!ops_per_s || iters <= 0 || mode < 0 || mode > 2) return DS_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -367,11 +287,7 @@ extern "C" int ds_pipe_peak(int mode, int iters, double* ops_per_s, void* stream
     auto run = [&](int n) {
         if (mode == 0) peak_kernel<0><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
         else if (mode == 1) peak_kernel<1><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
-        else if (mode == 2) peak_kernel<2><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
-        else if (mode == 3) peak2_kernel<3><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
-        else if (mode == 4) peak2_kernel<4><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
-        else if (mode == 5) peak3_kernel<5><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
-        else peak3_kernel<6><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
+        else peak_kernel<2><<<blocks, threads, 0, st>>>(n, 0x2b5a9, sink);
         note_launch();
     };
     run(iters / 8 + 1);  // warm-up
@@ -386,7 +302,7 @@ extern "C" int ds_pipe_peak(int mode, int iters, double* ops_per_s, void* stream
     cudaEventDestroy(e1);
     cudaFree(sink);
     if (rc == DS_OK && ms > 0.f)
-        *ops_per_s = double(blocks) * threads * double(iters) * 4.0 * kChains * (mode >= 3 ? 2.0 : 1.0) * (mode >= 5 ? 0.5 : 1.0) / (double(ms) * 1e-3);
+        *ops_per_s = double(blocks) * threads * double(iters) * 4.0 * kChains / (double(ms) * 1e-3);
     return rc;
 }
 

@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
         if (p.bias) v += __ldg(p.bias + n);
         if (p.residual) v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + o)));
         if (p.relu) v = max(v, 0);
-        if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi);
+        if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi) * p.rq_mul + p.rq_add;
         if (p.round_f32) v = __float2int_rn(__int2float_rn(v));
         if (p.out_kind == DS_OUT_I32) static_cast<int*>(p.out)[o] = v;
         else static_cast<float*>(p.out)[o] = __int2float_rn(v) * p.inv_scale;

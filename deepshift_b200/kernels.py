@@ -3,7 +3,8 @@
 ``linear``, ``conv2d`` and ``compress_sign_and_shift`` keep the names, argument order and
 return values of pytorch/deepshift/kernels/kernels.py:10,28,69.  They call the C ABI of
 include/deepshift_b200.h through ctypes on torch's current stream.  ``use_cuda=False`` raises:
-this package has no CPU path.
+this package has no CPU path.  Calls may be issued on several streams of a device at once: the
+scratch memory the kernels share along K is kept per (device, stream).
 
 Differences from the reference, all deliberate:
   * the convolution reads the unpadded tensor (no ``F.pad`` copy, no im2col/col2im buffers);
@@ -55,17 +56,36 @@ _WS_PARTIAL_INTS = 444 * 32768 + (8 << 20)  # expanded weights of one layer (32 
                                              # up to 444 (tile, split) slots of 128 KiB
 
 
-def workspace(device):
-    """Per-device scratch for sharing output tiles between CTAs along K (see
-    ds_fuse_t.workspace): zeroed arrival counters followed by room for partial sums.  Kernels
-    leave the counters zero, so one tensor serves every launch on the device's streams in order."""
+def workspace(device, stream=None):
+    """Scratch for sharing output tiles between CTAs along K (see ds_fuse_t.workspace): zeroed
+    arrival counters followed by room for expanded weights and partial sums.  One tensor per
+    (device, stream): launches that share a workspace must not overlap on the GPU, and launches on
+    one stream never do.  ``stream`` defaults to torch's current stream of ``device``.  Kernels leave
+    the counters zero, so the tensor serves every launch of its stream in order."""
     device = torch.device(device)
     if device.index is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    ws = _WORKSPACES.get(device)
+    if stream is None:
+        stream = torch.cuda.current_stream(device)
+    key = (device, int(stream.cuda_stream))
+    ws = _WORKSPACES.get(key)
     if ws is None:
-        ws = _WORKSPACES[device] = torch.zeros(_WS_COUNTERS + _WS_PARTIAL_INTS, dtype=torch.int32, device=device)
+        ws = _WORKSPACES[key] = new_workspace(device)
     return ws
+
+
+def new_workspace(device):
+    """A workspace of its own for a caller that manages streams itself (the integer pipeline keeps
+    one per instance, so two pipelines may run on two streams at once)."""
+    return torch.zeros(_WS_COUNTERS + _WS_PARTIAL_INTS, dtype=torch.int32, device=device)
+
+
+def last_kernel_error():
+    """1 if a kernel's bounded wait ran out since the last call (its output is then undefined), else
+    0.  Synchronises the current device and clears the flag."""
+    flag = ctypes.c_int(-1)
+    _ffi.check(_ffi.lib().ds_last_kernel_error(ctypes.byref(flag)), "last_kernel_error")
+    return flag.value
 
 
 def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=False, requant=False,

@@ -43,15 +43,33 @@ class _ShiftBase(nn.Module):
             self._bias_key = key
         return self._bias_i32
 
+    # ``conc_weight`` as the reference names it (modules.py:86,306).  Assigning it (convert_to_shift
+    # does, convert.py:39-40,75-76) hands over packed weights that match the parameters of that
+    # moment; the version key is taken at the next forward pass.
+    @property
+    def conc_weight(self):
+        return self.__dict__.get("_conc_weight")
+
+    @conc_weight.setter
+    def conc_weight(self, value):
+        self.__dict__["_conc_weight"] = value
+        self.__dict__["_weight_key"] = None
+
     def _packed(self, device):
-        # The reference leaves conc_weight to convert_to_shift (convert.py:39-40,75-76); a module
-        # built by hand gets it packed on first use.
-        if self.conc_weight is None:
+        """Packed weights that match the current ``shift`` / ``sign``: packed on first use when the
+        module was built by hand, and again whenever either parameter was replaced or changed in
+        place (``load_state_dict``, an optimiser step) since they were packed."""
+        key = (self.shift.data_ptr(), self.shift._version, self.sign.data_ptr(), self.sign._version)
+        cw, have = self.conc_weight, self.__dict__.get("_weight_key")
+        if cw is None or (have is not None and have != key):
             self.conc_weight = utils.compress_bits(self.shift.data.round(), self.sign.data.round().sign(),
                                                    device=device)
-        elif self.conc_weight.data.device != device:
-            self.conc_weight.data = self.conc_weight.data.to(device)
-        return self.conc_weight
+            cw = self.conc_weight
+        elif cw.data.device != device:
+            cw.data = cw.data.to(device)
+            cw.__dict__.pop("_prepared", None)   # expanded copies live on the old device
+        self.__dict__["_weight_key"] = key
+        return cw
 
     def _float_weight(self):
         shift_rounded = ste.round(self.shift, rounding=self.rounding)
@@ -199,16 +217,18 @@ class Conv2dShift(_ConvNdShift):
             if self.dilation != (1, 1) or self.groups != 1:
                 raise RuntimeError("the shift convolution kernel supports neither dilation nor groups")
             x = input.float().contiguous()
-            in_kind = _ffi.IN_F32_CONV
+            in_kind, act_bits = _ffi.IN_F32_CONV, 0
             if self.kernel_size[0] * self.kernel_size[1] >= 25:
-                # a large window reads every input value many times: quantise once, in its own pass
+                # a large window reads every input value many times: quantise once, in its own pass;
+                # the codes are final (round_to_fixed is not idempotent for one integer bit), so the
+                # kernel gets them as plain int32 with their bound
                 x = kernels.quantize(x, self.act_integer_bits, self.act_fraction_bits, like_conv=True)
-                in_kind = _ffi.IN_I32_CLAMP
+                in_kind, act_bits = _ffi.IN_I32, utils.code_bits(self.act_integer_bits, self.act_fraction_bits)
             return kernels.conv2d_fused(x, tuple(self.shift.shape), self._bias_fixed(like_conv=True),
                                         self._packed(x.device), self.stride, padding,
                                         in_kind=in_kind, out_kind=_ffi.OUT_F32,
                                         act_integer_bits=self.act_integer_bits,
-                                        act_fraction_bits=self.act_fraction_bits)
+                                        act_fraction_bits=self.act_fraction_bits, act_bits=act_bits)
         self.shift.data = ste.clamp(self.shift.data, *self.shift_range)
         input_fixed_point = ste.round_fixed_point(input, self.act_integer_bits, self.act_fraction_bits)
         bias_fixed_point = None

@@ -69,8 +69,8 @@ class _ShiftQBase(nn.Module):
                                 like_conv=True)
 
     def _act_bits(self):
-        # the codes are clamped to I + F bits, which is what the FP32-pipe path needs to know
-        return self.act_integer_bits + self.act_fraction_bits
+        # the bound on the codes, which is what the FP32-pipe path needs to know
+        return utils.code_bits(self.act_integer_bits, self.act_fraction_bits)
 
 
 class LinearShiftQ(_ShiftQBase):
@@ -207,15 +207,15 @@ class Conv2dShiftQ(_ConvNdShiftQ):
             if self.dilation != (1, 1) or self.groups != 1:
                 raise RuntimeError("the shift convolution kernel supports neither dilation nor groups")
             x = input.float().contiguous()
-            in_kind = _ffi.IN_F32_CONV
+            in_kind, act_bits = _ffi.IN_F32_CONV, 0
             if self.kernel_size[0] * self.kernel_size[1] >= 25:
                 # a large window reads every input value many times: quantise once, in its own pass
                 x = self._input_codes(x)
-                in_kind = _ffi.IN_I32_CLAMP
+                in_kind, act_bits = _ffi.IN_I32, self._act_bits()
             return kernels.conv2d_fused(x, tuple(self.weight.shape), self._bias_fixed(), self._packed(x.device),
                                         self.stride, padding, in_kind=in_kind, out_kind=_ffi.OUT_F32,
                                         act_integer_bits=self.act_integer_bits,
-                                        act_fraction_bits=self.act_fraction_bits)
+                                        act_fraction_bits=self.act_fraction_bits, act_bits=act_bits)
         weight_q = utils.round_power_of_2(self._clamped_weight(), self.rounding)
         input_fixed_point = utils.round_to_fixed(input, self.act_integer_bits, self.act_fraction_bits)
         bias_fixed_point = None

@@ -18,6 +18,12 @@ def round_to_fixed(input, integer_bits=16, fraction_bits=16):
     return torch.clamp(rounded, -bound, bound - 1)
 
 
+def code_bits(integer_bits, fraction_bits):
+    """Bits b such that every int32 code of round_to_fixed(., I, F) * 2^F lies in
+    [-2^(b-1), 2^(b-1)]: I + F, or F + 2 for one integer bit (codes -2^(F+1), -2^F, 0)."""
+    return fraction_bits + 2 if integer_bits == 1 else integer_bits + fraction_bits
+
+
 def round(x, rounding='deterministic'):
     """utils.py:36-42.  The misspelling 'determinstic' (Conv2dShift's default,
     modules.py:296) is accepted as 'deterministic'."""

@@ -9,9 +9,13 @@ residual bookkeeping).  The same program is run
 * by ``IntPipeline``: activations stay int32 fixed point from the first layer to the logits,
   ReLU / residual add / fp32 rounding are fused into the convolution epilogues, pooling runs on
   the int32 codes, all buffers are pre-allocated and the whole forward pass can be replayed as
-  one CUDA graph.  Every shift-layer output is bit-identical to ``ModuleNet``'s; the logits are
-  too, except where torch's CUDA average pool rounds differently from an exact sum divided once
-  (7x7 maps at full ImageNet resolution: a few logits move by 1-3 codes of 2^-12).
+  one CUDA graph.  Every shift-layer output and the logits are bit-identical to ``ModuleNet``'s.
+
+Global average pooling follows torch's CPU kernel, which the reference's CPU path runs: an fp32
+sum divided by H*W.  torch's CUDA ``adaptive_avg_pool2d`` multiplies the sum by a rounded 1/(H*W)
+instead, which moves a few logits of a 7x7 map by 1-3 codes of 2^-12; ``ModuleNet`` therefore
+writes the pooling as ``sum / (H*W)``, and ``IntPipeline`` computes the same from the exact integer
+sum (equal whenever a plane's codes sum to less than 2^24, where fp32 addition is exact).
 
 Topologies: the reference's ``LinearMNIST`` / ``ConvMNIST`` (pytorch/mnist.py:23-57, without the
 dropout and log-softmax, which are not part of the kernel path), its CIFAR-10 ``resnet20``
@@ -241,7 +245,9 @@ class ModuleNet(nn.Module):
             elif op == 'maxpool':
                 t['x'] = F.max_pool2d(t['x'], st[1], st[2], st[3])
             elif op == 'gap':
-                t['x'] = F.adaptive_avg_pool2d(t['x'], 1).flatten(1)
+                # fp32 sum, then a true division: what torch's CPU adaptive_avg_pool2d computes
+                x = t['x']
+                t['x'] = x.sum((2, 3)) / float(x.shape[2] * x.shape[3])
             elif op == 'flatten':
                 t['x'] = t['x'].flatten(1)
             elif op == 'copy':
@@ -269,6 +275,7 @@ class IntPipeline:
             self.packed.append(utils.compress_bits(w['shift'].float(), w['sign'].float(), device=self.device))
             self.bias.append((w['bias'] * (2 ** self.F)).int().to(self.device).contiguous())
         self.x_in = torch.empty((batch,) + net.in_shape, dtype=torch.float32, device=self.device)
+        self.workspace = kernels.new_workspace(self.device)   # its own: pipelines may run side by side
         self._plan()
         self._n_launches = None
         self.graph = None
@@ -313,7 +320,7 @@ class IntPipeline:
                 res = t[o['add']] if o.get('add') else None
                 fuse = kernels._fuse(in_kind, _ffi.OUT_F32 if lastlayer else _ffi.OUT_I32, self.I, self.F,
                                      relu=bool(o.get('relu')), requant=False, residual=res,
-                                     round_f32=not lastlayer, workspace=kernels.workspace(dev))
+                                     round_f32=not lastlayer, workspace=self.workspace)
                 self.calls.append((op, xin, li, L, out, fuse, res))
                 dst = o.get('dst', 'x')
                 t[dst], fp32[dst] = out, lastlayer

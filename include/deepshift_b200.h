@@ -49,7 +49,10 @@ enum {
     DS_IN_F32_LINEAR = 2,/* fp32, quantised as LinearShift does: trunc(x*2^F), no clamp -- modules.py:25 */
     DS_IN_I32_CLAMP = 3  /* int32 fixed point, clamped on read to [-2^(I-1+F), (2^(I-1)-1)*2^F]: what
                             Conv2dShift's round_to_fixed does to a value already on the 2^-F grid.
-                            Lets one unclamped tensor feed both a convolution and a residual add. */
+                            Lets one unclamped tensor feed both a convolution and a residual add.
+                            With I == 1 round_to_fixed is sign(x) - 1 (utils.py:12-13), so a code
+                            c < 0, c == 0, c > 0 is read as -2^(F+1), -2^F, 0: apply it to codes that
+                            have NOT been through round_to_fixed yet (it is not idempotent there). */
 };
 
 /* Output element kinds of the *_ex entry points. */
@@ -70,13 +73,16 @@ typedef struct {
     int act_fraction_bits;  /* F; used by every fp32 conversion                            */
     int relu;               /* v = max(v, 0)                                               */
     int requant;            /* v = clamp(v, -2^(I-1+F), (2^(I-1)-1)*2^F): what the next
-                               Conv2dShift's round_to_fixed would do to v/2^F              */
-    const int32_t *residual;/* same shape/layout as the output, added before ReLU; may be NULL */
+                               Conv2dShift's round_to_fixed would do to v/2^F (I == 1: the
+                               sign rule described at DS_IN_I32_CLAMP)                     */
+    const int32_t *residual;/* same shape/layout as the output, added before ReLU; may be NULL.  May be
+                               the int32 output buffer itself (in-place add); any other overlap with
+                               the output is not allowed                                   */
     int act_bits;           /* caller's guarantee on int32 inputs: every x satisfies
                                -2^(act_bits-1) <= x <= 2^(act_bits-1).  0 = no guarantee
                                (exact integer path).  1..20 enables the FP32-pipe path.
-                               Implied by DS_IN_F32_CONV and
-                               DS_IN_I32_CLAMP (I+F).                            */
+                               Implied by DS_IN_F32_CONV and DS_IN_I32_CLAMP (I+F, or F+2
+                               when I == 1).                                               */
     int round_f32;          /* v = int(float(v)): the rounding the reference's `out.float()` applies
                                to sums beyond 2^24, so that an int32 tensor handed to the next layer
                                holds exactly the value the reference's fp32 tensor would        */
@@ -196,8 +202,6 @@ int ds_avgpool_fix_i32(const int32_t *x, int32_t *out, int B, int C, int H, int 
  *   mode 0: shift + add (both on the integer ALU pipe)
  *   mode 1: shift + integer multiply-add (ALU pipe + FMA pipe)
  *   mode 2: FP32 fused multiply-add with round-down (FMA pipe)
- *   mode 3: packed FP32 pair fused multiply-add with round-down (fma.rm.f32x2, two terms each)
- *   mode 4: mode 3 with one independent integer instruction issued beside every packed FMA
  * Runs on `stream`, synchronises, and writes the sustained rate in shift-accumulate
  * operations per second (one op = one shift plus one signed accumulate) to *ops_per_s.
  */

@@ -8,7 +8,7 @@ result is the pybind module ``deepshift_cpu`` exporting ``linear_kernel`` and
 ``convolution_kernel`` (shift_cpu.cpp:376-379).  It is used to pin oracle/ds_oracle.c, to
 generate tests/golden/*.npz and as the timed "reference" CPU baseline.
 
-Usage: python oracle/build_ref.py [path-to-reference-checkout]
+Usage: python oracle/build_ref.py path-to-reference-checkout   (or DEEPSHIFT_REFERENCE in the environment)
 """
 import os
 import subprocess
@@ -26,10 +26,10 @@ def ref_module_path():
 
 def build(reference_root=None, force=False):
     """Returns the path of the built module, or None when the reference is not mounted."""
-    reference_root = reference_root or os.environ.get("DEEPSHIFT_REFERENCE", "/root/reference")
-    src = os.path.join(reference_root, SRC_REL)
+    reference_root = reference_root or os.environ.get("DEEPSHIFT_REFERENCE")
     out = ref_module_path()
-    if not os.path.exists(src):
+    src = os.path.join(reference_root, SRC_REL) if reference_root else None
+    if src is None or not os.path.exists(src):
         return out if os.path.exists(out) else None
     if os.path.exists(out) and not force and os.path.getmtime(out) >= os.path.getmtime(src):
         return out

@@ -187,6 +187,19 @@ def from_fixed(o, fraction_bits):
     return np.asarray(o, np.int32).astype(np.float32) / np.float32(2 ** fraction_bits)
 
 
+def global_avg(x):
+    """Global average pool of fp32 NCHW planes as torch computes it on the CPU for the reference's
+    ResNets (cifar10_models/resnet.py:122-134 ``F.avg_pool2d(out, out.size()[3])``; torchvision's
+    ``AdaptiveAvgPool2d(1)`` behind imagenet.py:199-219, which is ``mean`` over H and W): an fp32
+    sum followed by an IEEE division by H*W.  The sum is formed exactly (float64) and rounded
+    once; that equals torch's vectorised fp32 sum whenever the plane's sum of 2^-F codes stays
+    below 2^24 (pinned by tests/golden/gap_ref.npz).  Beyond that torch's own result depends on
+    the vector width of the CPU, and its CUDA kernel multiplies by a rounded 1/(H*W) instead."""
+    x = np.asarray(x, dtype=np.float32)
+    s = x.astype(np.float64).sum(axis=(2, 3)).astype(np.float32)
+    return (s / np.float32(x.shape[2] * x.shape[3])).astype(np.float32)
+
+
 def compress_bits(shift, sign):
     """Host half of the packing, utils.py:61-88, with the evident intent of lines 67-70
     (a weight whose sign is 0 becomes sign +1, shift -32) applied by mask on copies.

@@ -24,14 +24,6 @@ def _max_pool(x, k, s, p):
     return out
 
 
-def _global_avg(x):
-    # Sum of values on the 2^-F grid; float64 holds it exactly, one rounding to float32, then the
-    # float32 division torch performs.
-    B, C, H, W = x.shape
-    s = x.astype(np.float64).sum(axis=(2, 3)).astype(np.float32)
-    return (s / np.float32(H * W)).astype(np.float32)
-
-
 def forward(net, weights, x):
     """net: workloads.Net; weights: list of dicts with numpy 'shift', 'sign' (int32) and 'bias'
     (float32); x: float32 [B,C,H,W].  Returns float32 logits."""
@@ -62,7 +54,7 @@ def forward(net, weights, x):
         elif op == 'maxpool':
             t['x'] = _max_pool(t['x'], st[1], st[2], st[3])
         elif op == 'gap':
-            t['x'] = _global_avg(t['x'])
+            t['x'] = O.global_avg(t['x'])
         elif op == 'flatten':
             t['x'] = t['x'].reshape(t['x'].shape[0], -1)
         elif op == 'copy':

@@ -30,3 +30,15 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="session", autouse=True)
+def no_kernel_wait_ran_out():
+    """After the whole session: no kernel of the library gave up on one of its bounded waits (such
+    a launch would have produced undefined output without any other sign)."""
+    yield
+    import torch
+    if torch.cuda.is_available():
+        from deepshift_b200 import _ffi, kernels
+        if _ffi._lib is not None:
+            assert kernels.last_kernel_error() == 0

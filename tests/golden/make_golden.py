@@ -11,8 +11,11 @@ Two sources, both executed in a container where the reference checkout is mounte
 
 Inputs are seeded; each file stores inputs and the reference's outputs.
 
-Usage: python tests/golden/make_golden.py [--only-q] [path-to-reference-checkout]
-(--only-q: write q_ref.npz, the DeepShift-Q module vectors, and leave the other files alone)
+Usage: python tests/golden/make_golden.py [--only-q | --only-sign | --only-gap] path-to-reference-checkout
+(--only-q: write q_ref.npz, the DeepShift-Q module vectors, and leave the other files alone;
+ --only-sign: write sign_ref.npz, modules with one integer bit; --only-gap: write gap_ref.npz, the
+ average-pool glue, which needs torch only).  The checkout path may also come from the environment
+variable DEEPSHIFT_REFERENCE.
 """
 import os
 import sys
@@ -75,6 +78,67 @@ def main_q(reference_root):
     out["n"] = np.int32(3)
     np.savez_compressed(os.path.join(HERE, "q_ref.npz"), **out)
     print("q_ref.npz", os.path.getsize(os.path.join(HERE, "q_ref.npz")), "bytes")
+
+
+def main_sign(reference_root):
+    """sign_ref.npz: forward passes of the reference's Conv2dShift and Conv2dShiftQ with
+    act_integer_bits = 1, where round_to_fixed is sign(x) - 1 (utils.py:12-13), on windows of 25 and
+    49 taps, use_kernel=True on the reference's CPU kernel.  padding = 0 and no zero weights for the
+    reasons given at main_q."""
+    assert build_ref.build(reference_root) is not None, "reference checkout not found"
+    _import_reference(reference_root)
+    import deepshift.modules as ref_modules
+    import deepshift.modules_q as ref_q
+    out = {}
+    rng = np.random.default_rng(5000)
+    cases = [("ps", 3, 6, 5, 1, 12, 7), ("ps", 2, 5, 7, 2, 17, 12), ("q", 3, 4, 5, 1, 11, 7), ("q", 2, 6, 7, 2, 16, 10)]
+    for i, (kind, cin, cout, k, stride, hw, F) in enumerate(cases):
+        torch.manual_seed(50 + i)
+        xin = rng.normal(0, 1, (2, cin, hw, hw)).astype(np.float32)
+        xin[rng.random(xin.shape) < 0.15] = 0.0      # exact zeros: the middle code -2^F
+        xin = torch.from_numpy(xin)
+        if kind == "ps":
+            conv = ref_modules.Conv2dShift(cin, cout, k, stride=stride, padding=0, bias=True, use_kernel=True,
+                                           use_cuda=False, rounding="deterministic", act_integer_bits=1,
+                                           act_fraction_bits=F)
+            conv.shift.data = torch.from_numpy(rng.integers(-14, 1, (cout, cin, k, k)).astype(np.float32))
+            conv.sign.data = torch.from_numpy(rng.choice([-1.0, 1.0], (cout, cin, k, k)).astype(np.float32))
+            out[f"shift{i}"], out[f"sign{i}"] = conv.shift.data.numpy().copy(), conv.sign.data.numpy().copy()
+        else:
+            conv = ref_q.Conv2dShiftQ(cin, cout, k, stride=stride, padding=0, bias=True, use_kernel=True,
+                                      use_cuda=False, act_integer_bits=1, act_fraction_bits=F)
+            out[f"w{i}"] = conv.weight.data.numpy().copy()
+        out[f"kind{i}"], out[f"bias{i}"] = np.array(kind), conv.bias.data.numpy().copy()
+        out[f"x{i}"], out[f"stride{i}"], out[f"F{i}"] = xin.numpy().copy(), np.int32(stride), np.int32(F)
+        with torch.no_grad():
+            out[f"y{i}"] = conv(xin.clone()).numpy()
+    out["n"] = np.int32(len(cases))
+    np.savez_compressed(os.path.join(HERE, "sign_ref.npz"), **out)
+    print("sign_ref.npz", os.path.getsize(os.path.join(HERE, "sign_ref.npz")), "bytes")
+
+
+def main_gap():
+    """gap_ref.npz: the glue between the last convolution and the classifier of the reference's
+    ResNets (cifar10_models/resnet.py:122-134, torchvision's ResNet via imagenet.py:199-219):
+    torch's CPU ``F.adaptive_avg_pool2d(x, 1)`` on fp32 planes of values on the 2^-12 grid, then the
+    LinearShift entry conversion ``(x * 2^F).int()`` (modules.py:25).  Plane sums stay below 2^24
+    codes, where fp32 summation is exact in any order; beyond that torch's own CPU result depends
+    on the vector width of the machine and its CUDA kernel multiplies by a rounded reciprocal."""
+    import torch.nn.functional as Fnn
+    out = {}
+    rng = np.random.default_rng(6000)
+    cases = [(7, 1 << 16), (7, 1 << 18), (8, 1 << 17), (4, 1 << 19), (14, 1 << 16), (1, 1 << 23)]
+    for i, (hw, top) in enumerate(cases):
+        codes = rng.integers(-(top // 8), top, (3, 24, hw, hw)).astype(np.int32)
+        codes[0] = np.maximum(codes[0], 0)                      # what follows a ReLU
+        x = torch.from_numpy(codes.astype(np.float32) / np.float32(4096))
+        pooled = Fnn.adaptive_avg_pool2d(x, 1).flatten(1)
+        out[f"codes{i}"] = codes
+        out[f"pooled{i}"] = pooled.numpy().copy()
+        out[f"fixed{i}"] = (pooled * (2 ** 12)).int().numpy().copy()
+    out["n"], out["F"] = np.int32(len(cases)), np.int32(12)
+    np.savez_compressed(os.path.join(HERE, "gap_ref.npz"), **out)
+    print("gap_ref.npz", os.path.getsize(os.path.join(HERE, "gap_ref.npz")), "bytes")
 
 
 def main(reference_root):
@@ -161,8 +225,19 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    args = [a for a in sys.argv[1:] if a != "--only-q"]
-    root = args[0] if args else os.environ.get("DEEPSHIFT_REFERENCE", "/root/reference")
-    if "--only-q" not in sys.argv:
+    flags = [a for a in sys.argv[1:] if a.startswith("--only-")]
+    args = [a for a in sys.argv[1:] if not a.startswith("--only-")]
+    root = args[0] if args else os.environ.get("DEEPSHIFT_REFERENCE")
+    if flags == ["--only-gap"]:
+        main_gap()
+        sys.exit(0)
+    if not root:
+        sys.exit("give the path of the reference checkout (argument or DEEPSHIFT_REFERENCE)")
+    if not flags:
         main(root)
-    main_q(root)
+    if not flags or "--only-q" in flags:
+        main_q(root)
+    if not flags or "--only-sign" in flags:
+        main_sign(root)
+    if not flags or "--only-gap" in flags:
+        main_gap()

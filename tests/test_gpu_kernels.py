@@ -690,3 +690,155 @@ def test_random_shapes_against_oracle(oracle, cuda_device):
                                    in_kind=_ffi.IN_I32_CLAMP, out_kind=_ffi.OUT_F32, act_integer_bits=4,
                                    act_fraction_bits=12, relu=True)
         assert np.array_equal(out.cpu().numpy(), oracle.from_fixed(np.maximum(ref, 0), 12)), tag
+
+
+# ----------------------------------------------------------------------------------------- one integer bit
+def test_sign_mode_modules_match_reference_golden(cuda_device, golden_dir):
+    """act_integer_bits = 1 (round_to_fixed = sign(x) - 1) on 5x5 and 7x7 windows, where the modules
+    quantise in a pass of their own: forward passes recorded from the reference's Conv2dShift and
+    Conv2dShiftQ."""
+    from deepshift_b200 import modules, modules_q
+    g = np.load(os.path.join(golden_dir, "sign_ref.npz"))
+    for i in range(int(g["n"])):
+        F, st = int(g[f"F{i}"]), int(g[f"stride{i}"])
+        if str(g[f"kind{i}"]) == "ps":
+            sh = g[f"shift{i}"]
+            conv = modules.Conv2dShift(sh.shape[1], sh.shape[0], sh.shape[2], stride=st, padding=0, use_kernel=True,
+                                       rounding="deterministic", act_integer_bits=1, act_fraction_bits=F).to(cuda_device)
+            conv.shift.data, conv.sign.data = _t(sh, cuda_device), _t(g[f"sign{i}"], cuda_device)
+        else:
+            w = g[f"w{i}"]
+            conv = modules_q.Conv2dShiftQ(w.shape[1], w.shape[0], w.shape[2], stride=st, padding=0, use_kernel=True,
+                                          act_integer_bits=1, act_fraction_bits=F).to(cuda_device)
+            conv.weight.data = _t(w, cuda_device)
+        conv.bias.data = _t(g[f"bias{i}"], cuda_device)
+        assert np.array_equal(conv(_t(g[f"x{i}"], cuda_device)).cpu().numpy(), g[f"y{i}"]), i
+
+
+@pytest.mark.parametrize("F", [7, 12])
+def test_sign_mode_on_int32_codes_matches_oracle(oracle, cuda_device, F):
+    """One integer bit on the int32 input kinds: DS_IN_I32_CLAMP and `requant` apply
+    round_to_fixed(code / 2^F, 1, F) = sign - 1 to codes that have not been quantised yet; a 3x3
+    Conv2dShift (quantiser fused into the staging) and LinearShiftQ give the same as the oracle."""
+    from deepshift_b200 import _ffi, kernels, modules, modules_q, utils
+    rng = np.random.default_rng(100 + F)
+    B, C, H, OC = 3, 20, 9, 70
+    codes = rng.integers(-3, 4, (B, C, H, H)).astype(np.int32) * rng.integers(1, 1 << 20, (B, C, H, H)).astype(np.int32)
+    shift, sign = weights(rng, (OC, C, 3, 3))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    xq = oracle.to_fixed_conv(oracle.from_fixed(codes, F), 1, F)
+    assert np.array_equal(xq, np.where(codes > 0, 0, np.where(codes < 0, -(2 << F), -(1 << F))))
+    acc = oracle.conv2d(xq, shift, sign, bias, (1, 1), (1, 1))
+    rq = np.where(acc > 0, 0, np.where(acc < 0, -(2 << F), -(1 << F))).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    out = kernels.conv2d_fused(_t(codes, cuda_device), (OC, C, 3, 3), _t(bias, cuda_device), cw, 1, 1,
+                               in_kind=_ffi.IN_I32_CLAMP, act_integer_bits=1, act_fraction_bits=F)
+    assert np.array_equal(out.cpu().numpy(), acc)
+    out = kernels.conv2d_fused(_t(codes, cuda_device), (OC, C, 3, 3), _t(bias, cuda_device), cw, 1, 1,
+                               in_kind=_ffi.IN_I32_CLAMP, act_integer_bits=1, act_fraction_bits=F, requant=True)
+    assert np.array_equal(out.cpu().numpy(), rq)
+    # modules: fused quantiser (3x3) and the DeepShift-Q linear layer
+    xf = rng.normal(0, 1, (B, C, H, H)).astype(np.float32)
+    xf[rng.random(xf.shape) < 0.2] = 0.0
+    conv = modules.Conv2dShift(C, OC, 3, padding=1, use_kernel=True, rounding="deterministic", act_integer_bits=1,
+                               act_fraction_bits=F).to(cuda_device)
+    conv.shift.data, conv.sign.data = _t(shift.astype(np.float32), cuda_device), _t(sign.astype(np.float32), cuda_device)
+    bi = oracle.to_fixed_conv(conv.bias.data.cpu().numpy(), 1, F)
+    ref = oracle.conv2d(oracle.to_fixed_conv(xf, 1, F), shift, sign, bi, (1, 1), (1, 1))
+    assert np.array_equal(conv(_t(xf, cuda_device)).cpu().numpy(), oracle.from_fixed(ref, F))
+    torch.manual_seed(F)
+    lin = modules_q.LinearShiftQ(300, 70, use_kernel=True, act_integer_bits=1, act_fraction_bits=F).to(cuda_device)
+    xl = rng.normal(0, 1, (130, 300)).astype(np.float32)
+    sh, sg = utils.get_shift_and_sign(lin.weight.data.cpu())
+    ref = oracle.linear(oracle.to_fixed_conv(xl, 1, F), sh.numpy().astype(np.int32), sg.numpy().astype(np.int32),
+                        oracle.to_fixed_conv(lin.bias.data.cpu().numpy(), 1, F))
+    assert np.array_equal(lin(_t(xl, cuda_device)).cpu().numpy(), oracle.from_fixed(ref, F))
+
+
+def test_global_average_kernel_matches_torch_golden(cuda_device, golden_dir):
+    """ds_avgpool_fix_i32 against torch's CPU adaptive_avg_pool2d followed by the LinearShift entry
+    conversion, recorded in gap_ref.npz."""
+    from deepshift_b200 import kernels
+    g = np.load(os.path.join(golden_dir, "gap_ref.npz"))
+    for i in range(int(g["n"])):
+        got = kernels.avgpool_fix_i32(_t(g[f"codes{i}"], cuda_device), int(g["F"]))
+        assert np.array_equal(got.cpu().numpy(), g[f"fixed{i}"]), i
+
+
+def test_residual_may_alias_the_output(oracle, cuda_device):
+    """An in-place residual add (residual == out) on a shape that would otherwise be split along K
+    through the zeroed output."""
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(515)
+    B, C, H, OC = 5, 128, 7, 130
+    x = acts_q16(rng, (B, C, H, H))
+    shift, sign = weights(rng, (OC, C, 3, 3))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    res = rng.integers(-50000, 50000, (B, OC, H, H)).astype(np.int32)
+    ref = oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1))
+    ref = (ref.astype(np.float32) + res.astype(np.float32)).astype(np.int64).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    counters = torch.zeros(16384, dtype=torch.int32, device=cuda_device)   # counters only: the atomics scheme
+    for ws in (None, counters):
+        buf = _t(res, cuda_device)
+        f = kernels._fuse(_ffi.IN_I32_CLAMP, _ffi.OUT_I32, 4, 12, residual=buf, workspace=ws)
+        rc = _ffi.lib().ds_conv2d_ex(_t(x, cuda_device).data_ptr(), cw.data.data_ptr(), _t(bias, cuda_device).data_ptr(),
+                                     buf.data_ptr(), B, C, H, H, OC, 3, 3, 1, 1, 1, 1, cw.bits, cw.base, f,
+                                     torch.cuda.current_stream(cuda_device).cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize(cuda_device)
+        assert np.array_equal(buf.cpu().numpy(), ref)
+
+
+def test_two_streams_run_side_by_side(oracle, cuda_device):
+    """Two different convolutions issued on two streams with nothing ordering them: each stream has
+    its own scratch memory, so both results are exact (shapes that share tiles along K)."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(909)
+    cases = []
+    for (B, C, H, OC) in [(5, 128, 7, 130), (49, 32, 28, 100)]:
+        x = acts_q16(rng, (B, C, H, H))
+        shift, sign = weights(rng, (OC, C, 3, 3))
+        bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+        cases.append((_t(x, cuda_device), _t(shift, cuda_device), _t(bias, cuda_device), _cw(shift, sign, cuda_device),
+                      oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1))))
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in cases]
+    torch.cuda.synchronize(cuda_device)
+    assert kernels.workspace(cuda_device, streams[0]).data_ptr() != kernels.workspace(cuda_device, streams[1]).data_ptr()
+    outs = [[], []]
+    for _ in range(6):
+        for i, (x, shift, bias, cw, _) in enumerate(cases):
+            with torch.cuda.stream(streams[i]):
+                outs[i].append(kernels.conv2d(x, shift, None, bias, cw, 1, 1, act_bits=16))
+    torch.cuda.synchronize(cuda_device)
+    for i, c in enumerate(cases):
+        for o in outs[i]:
+            assert np.array_equal(o.cpu().numpy(), c[4]), i
+    assert kernels.last_kernel_error() == 0
+
+
+def test_ps_module_repacks_when_parameters_change(oracle, cuda_device):
+    """forward, load_state_dict, forward: the second pass uses the loaded weights (the packed copy
+    is keyed on the parameters' versions), and equals a module built fresh from them."""
+    from deepshift_b200 import modules
+    rng = np.random.default_rng(31)
+    kw = dict(use_kernel=True, rounding="deterministic", act_integer_bits=4, act_fraction_bits=12)
+    a = modules.Conv2dShift(8, 40, 3, padding=1, **kw).to(cuda_device)
+    b = modules.Conv2dShift(8, 40, 3, padding=1, **kw).to(cuda_device)
+    for m in (a, b):
+        shift, sign = weights(rng, (40, 8, 3, 3))
+        m.shift.data, m.sign.data = _t(shift.astype(np.float32), cuda_device), _t(sign.astype(np.float32), cuda_device)
+    x = _t(rng.normal(0, 1, (2, 8, 10, 10)).astype(np.float32), cuda_device)
+    ya, yb = a(x), b(x)
+    assert not torch.equal(ya, yb)
+    a.load_state_dict(b.state_dict())
+    assert torch.equal(a(x), yb)
+    a.sign.data.neg_()                       # in place: the version counter moves
+    fresh = modules.Conv2dShift(8, 40, 3, padding=1, **kw).to(cuda_device)
+    fresh.load_state_dict(a.state_dict())
+    assert torch.equal(a(x), fresh(x)) and not torch.equal(a(x), yb)
+    lin = modules.LinearShift(30, 70, **kw).to(cuda_device)
+    xl = _t(rng.normal(0, 1, (65, 30)).astype(np.float32), cuda_device)
+    y0 = lin(xl)
+    lin.shift.data.sub_(1.0)
+    assert not torch.equal(lin(xl), y0)

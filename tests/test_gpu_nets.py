@@ -29,15 +29,21 @@ def test_networks_bit_exact_against_oracle(oracle, cuda_device, name, batch, kw)
 
 
 def test_resnet18_full_resolution_sample_against_oracle(oracle, cuda_device):
-    """Two 224x224 images through the CPU oracle (a few seconds) against the pipeline."""
+    """Eight 224x224 images (the benchmark shape) through the CPU oracle against both product paths:
+    the drop-in modules with fp32 glue and the integer pipeline, and the two against each other."""
     from deepshift_b200 import workloads as W
     from oracle import reference_nets as R
     net = W.resnet18()
     ws = W.make_weights(net)
-    x = W.make_input(net, 2)
+    x = W.make_input(net, 8)
     ref = R.forward(net, np_weights(ws), x.numpy())
-    pipe = W.IntPipeline(net, ws, 2, cuda_device)
-    assert np.array_equal(pipe.run(x.to(cuda_device)).cpu().numpy(), ref)
+    pipe = W.IntPipeline(net, ws, 8, cuda_device)
+    y_pipe = pipe.run(x.to(cuda_device)).cpu().numpy()
+    with torch.no_grad():
+        y_mod = W.ModuleNet(net, ws, cuda_device).eval()(x.to(cuda_device)).cpu().numpy()
+    assert np.array_equal(y_pipe, ref)
+    assert np.array_equal(y_mod, ref)
+    assert np.array_equal(y_mod, y_pipe)
 
 
 def test_resnet18_benchmark_batch_properties(cuda_device):

@@ -45,6 +45,38 @@ def test_float_glue_matches_reference_golden(oracle, golden_dir):
     assert np.array_equal(y, g["conv_y"])
 
 
+def test_sign_mode_modules_of_the_reference_match_the_oracle(oracle, golden_dir):
+    """act_integer_bits = 1: round_to_fixed is sign(x) - 1 (utils.py:12-13), codes -2^(F+1), -2^F, 0.
+    Forward passes of the reference's Conv2dShift and Conv2dShiftQ (5x5 and 7x7 windows) restated."""
+    import torch
+    from deepshift_b200 import utils
+    g = np.load(os.path.join(golden_dir, "sign_ref.npz"))
+    for i in range(int(g["n"])):
+        F, st = int(g[f"F{i}"]), int(g[f"stride{i}"])
+        if str(g[f"kind{i}"]) == "ps":
+            shift, sign = g[f"shift{i}"].astype(np.int32), g[f"sign{i}"].astype(np.int32)
+        else:
+            w = utils.clampabs(torch.from_numpy(g[f"w{i}"].copy()), 2.0 ** -15, 1.0)
+            sh, sg = utils.get_shift_and_sign(w)
+            shift, sign = sh.numpy().astype(np.int32), sg.numpy().astype(np.int32)
+        xi = oracle.to_fixed_conv(g[f"x{i}"], 1, F)
+        assert set(np.unique(xi)) <= {-(2 << F), -(1 << F), 0}
+        ref = oracle.conv2d(xi, shift, sign, oracle.to_fixed_conv(g[f"bias{i}"], 1, F), (st, st), (0, 0))
+        assert np.array_equal(oracle.from_fixed(ref, F), g[f"y{i}"]), i
+
+
+def test_global_average_glue_matches_torch_golden(oracle, golden_dir):
+    """The pooling glue between the last convolution and the classifier: torch's CPU
+    adaptive_avg_pool2d followed by the LinearShift entry conversion (modules.py:25)."""
+    g = np.load(os.path.join(golden_dir, "gap_ref.npz"))
+    F = int(g["F"])
+    for i in range(int(g["n"])):
+        x = oracle.from_fixed(g[f"codes{i}"], F)
+        pooled = oracle.global_avg(x)
+        assert np.array_equal(pooled, g[f"pooled{i}"]), i
+        assert np.array_equal(oracle.to_fixed_linear(pooled, F), g[f"fixed{i}"]), i
+
+
 def test_against_compiled_reference_when_present(oracle):
     if oracle.ref_module() is None:
         pytest.skip("oracle/_ref not built (reference checkout not mounted)")

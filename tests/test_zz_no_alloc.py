@@ -35,22 +35,33 @@ def _run(entry, x, packed, bias, res, out, shape, cw, out_kind, dev):
                                    (40, 32, 28, 64, 3, 1, 1),     # plenty of tiles: no split
                                    (3, 64, 14, 256, 1, 2, 0)])    # 1x1 stride 2
 @pytest.mark.parametrize("out_f32", [False, True])
-def test_noalloc_matches_existing_entry_point_twice(cuda_device, shape, out_f32):
+def test_noalloc_matches_existing_entry_point_twice(oracle, cuda_device, shape, out_f32):
     """Bit-identical to ds_conv2d_ex (the tolerance of every other test here: none), on two calls
-    in a row -- the second one finds the array as the first left it."""
+    in a row -- the second one finds the array as the first left it.  Both are also held against the
+    CPU oracle, so the scheme this entry point is limited to (counters only: integer atomics on the
+    zeroed output) is anchored on its own."""
     from deepshift_b200 import _ffi, utils
     B, C, H, OC, k, s, p = shape
     rng = np.random.default_rng(sum(shape) + out_f32)
     OHW = (H + 2 * p - k) // s + 1
-    x = torch.from_numpy(acts_q16(rng, (B, C, H, H)) * 2).to(cuda_device)  # beyond the clamp: exercises IN_I32_CLAMP
+    x_np = acts_q16(rng, (B, C, H, H)) * 2                                 # beyond the clamp: exercises IN_I32_CLAMP
+    x = torch.from_numpy(x_np).to(cuda_device)
     shift, sign = weights(rng, (OC, C, k, k))
     cw = utils.compress_bits(torch.from_numpy(shift).float(), torch.from_numpy(sign).float(), device=cuda_device)
-    bias = torch.from_numpy(rng.integers(-2000, 2000, OC).astype(np.int32)).to(cuda_device)
-    res = torch.from_numpy(rng.integers(-50000, 50000, (B, OC, OHW, OHW)).astype(np.int32)).to(cuda_device)
+    bias_np = rng.integers(-2000, 2000, OC).astype(np.int32)
+    res_np = rng.integers(-50000, 50000, (B, OC, OHW, OHW)).astype(np.int32)
+    bias, res = torch.from_numpy(bias_np).to(cuda_device), torch.from_numpy(res_np).to(cuda_device)
     kind = _ffi.OUT_F32 if out_f32 else _ffi.OUT_I32
     dtype = torch.float32 if out_f32 else torch.int32
     want = torch.empty((B, OC, OHW, OHW), dtype=dtype, device=cuda_device)
     assert _run("ds_conv2d_ex", x, cw.data, bias, res, want, shape, cw, kind, cuda_device) == 0
+    # oracle: clamp of the 4.12 quantiser on read, integer convolution, fp32 residual add, ReLU,
+    # the rounding of `out.float()`, optional conversion to fp32
+    acc = oracle.conv2d(np.clip(x_np, -32768, 28672), shift, sign, bias_np, (s, s), (p, p))
+    ref = np.maximum(acc.astype(np.float32) + res_np.astype(np.float32), 0).astype(np.int64).astype(np.int32)
+    ref = ref.astype(np.float32).astype(np.int64).astype(np.int32)
+    ref = oracle.from_fixed(ref, 12) if out_f32 else ref
+    assert np.array_equal(want.cpu().numpy(), ref)
     for call in range(2):
         got = torch.full_like(want, 7)
         assert _run("ds_conv2d_noalloc", x, cw.data, bias, res, got, shape, cw, kind, cuda_device) == 0
