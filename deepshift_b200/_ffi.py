@@ -26,6 +26,22 @@ class Fuse(ctypes.Structure):
     ]
 
 
+class Staged(ctypes.Structure):
+    """Mirror of ``ds_staged_t``."""
+    _fields_ = [("data", ctypes.c_void_p), ("B", ctypes.c_int), ("H", ctypes.c_int), ("W", ctypes.c_int),
+                ("C", ctypes.c_int), ("halo", ctypes.c_int)]
+
+
+class StagedOut(ctypes.Structure):
+    """Mirror of ``ds_staged_out_t``."""
+    _fields_ = [
+        ("codes", ctypes.c_void_p), ("f32", ctypes.c_void_p), ("nchw", ctypes.c_void_p),
+        ("nchw_is_f32", ctypes.c_int), ("staged", ctypes.POINTER(Staged)), ("residual", ctypes.c_void_p),
+        ("relu", ctypes.c_int), ("round_f32", ctypes.c_int), ("act_integer_bits", ctypes.c_int),
+        ("act_fraction_bits", ctypes.c_int), ("in_act_bits", ctypes.c_int), ("reserved", ctypes.c_int * 3),
+    ]
+
+
 IN_I32, IN_F32_CONV, IN_F32_LINEAR, IN_I32_CLAMP = 0, 1, 2, 3
 OUT_I32, OUT_F32 = 0, 1
 
@@ -43,6 +59,12 @@ _SIGNATURES = {
     "ds_avgpool_fix_i32": [_VP, _VP, _I, _I, _I, _I, _I, _VP],
     "ds_pipe_peak": [_I, _I, ctypes.POINTER(ctypes.c_double), _VP],
     "ds_last_kernel_error": [ctypes.POINTER(ctypes.c_int)],
+    "ds_staged_fill": [ctypes.POINTER(Staged), _VP],
+    "ds_stage_nchw": [_VP, _I, _I, _I, ctypes.POINTER(Staged), _VP],
+    "ds_staged_prepare": [_VP, _I, _I, _I, _I, _I, _I, _VP, _LL, ctypes.POINTER(ctypes.c_longlong), _VP],
+    "ds_staged_conv2d": [ctypes.POINTER(Staged), _VP, _LL, _VP] + [_I] * 7 + [ctypes.POINTER(StagedOut), _VP, _LL, _VP],
+    "ds_maxpool_nhwc": [_VP] + [_I] * 7 + [_VP, ctypes.POINTER(Staged), _I, _I, _VP],
+    "ds_avgpool_fix_nhwc": [_VP, _VP, _I, _I, _I, _I, _I, _VP],
 }
 
 
@@ -66,6 +88,8 @@ def lib():
         l.ds_version.restype = ctypes.c_int
         l.ds_launch_count.argtypes = []
         l.ds_launch_count.restype = ctypes.c_longlong
+        l.ds_staged_bytes.argtypes = [_I] * 5
+        l.ds_staged_bytes.restype = ctypes.c_longlong
         _lib = l
     return _lib
 

@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     // the image or the matrix carry a marker so that stash() stores the integer 0 there
     // without quantising it.
     auto fetch = [&](int tile, int buf) {
-        const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
+        const int padv = p.pad_raw;
         if (ROW) {
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
@@ -598,6 +598,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.rq_lo = int(lo);
         p.rq_hi = int(hi);
     }
+    p.pad_raw = (f.in_kind == DS_IN_I32) ? 0 : (in_clamp ? (sign_mode ? 1 : 0) : kPadMarker);
     p.in_mul2 = int(2u * unsigned(p.rq_mul));
     p.in_add2 = int(2u * unsigned(p.rq_add) + unsigned(kHalfMagicBits + 1));
     // FP32-pipe path: needs base == 0, every |x| <= 2^(act_bits-1) <= 2^17, and room for at

@@ -72,6 +72,8 @@ struct GemmParams {
     // code' = clamp(code, rq_lo, rq_hi) * rq_mul + rq_add.  I >= 2: the clamp alone (mul 1, add 0).
     // I == 1 (utils.py:12-13, sign(x) - 1): clamp to [-1, 1], times 2^F, minus 2^F.
     int rq_lo, rq_hi, rq_mul, rq_add;
+    int pad_raw;  // what a position outside the image or matrix is read as, so that its code is 0: 0 for
+                  // int32 codes, 1 under the sign rule (code' of 1 is 0), kPadMarker for fp32 inputs
     int in_mul2, in_add2;  // FP path: float bits of 1.5*2^22 + code' + 0.5 = clamp * in_mul2 + in_add2
     float inv_scale;  // 2^-F
 };

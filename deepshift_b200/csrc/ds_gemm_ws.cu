@@ -4,6 +4,9 @@
 #include "ds_gemm_common.cuh"
 
 namespace ds {
+
+int* kernel_error_flag();
+
 namespace {
 
 __device__ int g_ws_error = 0;  // never set in a correct run
@@ -12,20 +15,26 @@ int* g_ws_error_ptr[kMaxDevices];  // device address of the flag, looked up once
 
 }  // namespace
 
-int launch_ws(const GemmParams& p0, int am, cudaStream_t st)
+int* kernel_error_flag()
 {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DS_ERR_CUDA;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     if (!g_ws_error_ptr[dev]) {
         void* ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_ws_error) != cudaSuccess || !ptr) {
             cudaGetLastError();
-            return DS_ERR_CUDA;
+            return nullptr;
         }
         g_ws_error_ptr[dev] = static_cast<int*>(ptr);
     }
+    return g_ws_error_ptr[dev];
+}
+
+int launch_ws(const GemmParams& p0, int am, cudaStream_t st)
+{
     GemmParams p = p0;
-    p.err_flag = g_ws_error_ptr[dev];
+    p.err_flag = kernel_error_flag();
+    if (!p.err_flag) return DS_ERR_CUDA;
     switch (am) {
         case AM_LINEAR: return launch_ws_linear(p, st);
         case AM_TABLE: return launch_ws_table(p, st);

@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // Issues the global loads of one k-tile into registers.  Positions outside the image or
         // the matrix get `padv` (0, or the marker that stands for an unquantised 0 for fp32 kinds).
         auto issue_loads = [&](int tile, int m0) {
-            const int padv = (p.in_kind == DS_IN_I32 || p.in_kind == DS_IN_I32_CLAMP) ? 0 : kPadMarker;
+            const int padv = p.pad_raw;
             if (!PRE) {
                 const int w0 = tile * p.kt_words;
 #pragma unroll

@@ -58,7 +58,8 @@ class _ShiftBase(nn.Module):
     def _packed(self, device):
         """Packed weights that match the current ``shift`` / ``sign``: packed on first use when the
         module was built by hand, and again whenever either parameter was replaced or changed in
-        place (``load_state_dict``, an optimiser step) since they were packed."""
+        place (``load_state_dict``, an optimiser step) since they were packed.  An in-place edit
+        through ``.data`` does not move the version counter: set ``conc_weight = None`` after one."""
         key = (self.shift.data_ptr(), self.shift._version, self.sign.data_ptr(), self.sign._version)
         cw, have = self.conc_weight, self.__dict__.get("_weight_key")
         if cw is None or (have is not None and have != key):

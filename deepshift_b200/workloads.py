@@ -11,11 +11,13 @@ residual bookkeeping).  The same program is run
   the int32 codes, all buffers are pre-allocated and the whole forward pass can be replayed as
   one CUDA graph.  Every shift-layer output and the logits are bit-identical to ``ModuleNet``'s.
 
-Global average pooling follows torch's CPU kernel, which the reference's CPU path runs: an fp32
-sum divided by H*W.  torch's CUDA ``adaptive_avg_pool2d`` multiplies the sum by a rounded 1/(H*W)
-instead, which moves a few logits of a 7x7 map by 1-3 codes of 2^-12; ``ModuleNet`` therefore
-writes the pooling as ``sum / (H*W)``, and ``IntPipeline`` computes the same from the exact integer
-sum (equal whenever a plane's codes sum to less than 2^24, where fp32 addition is exact).
+Global average pooling: fp32 summation order is not fixed by torch (its CPU kernel sums in an
+order that depends on the vector width, its CUDA ``adaptive_avg_pool2d`` reduces as a tree and then
+multiplies by a rounded 1/(H*W)), so results differ between the two by a few codes of 2^-12 once a
+plane's codes sum to more than 2^24 -- which the unclamped residual stream of this synthetic
+ResNet-18 does.  Both executors use the order-independent rule: the exact sum, rounded once to
+fp32, divided by H*W.  It equals torch's CPU result whenever fp32 addition is exact (sum of codes
+below 2^24; pinned by a golden vector).
 
 Topologies: the reference's ``LinearMNIST`` / ``ConvMNIST`` (pytorch/mnist.py:23-57, without the
 dropout and log-softmax, which are not part of the kernel path), its CIFAR-10 ``resnet20``
@@ -245,9 +247,11 @@ class ModuleNet(nn.Module):
             elif op == 'maxpool':
                 t['x'] = F.max_pool2d(t['x'], st[1], st[2], st[3])
             elif op == 'gap':
-                # fp32 sum, then a true division: what torch's CPU adaptive_avg_pool2d computes
+                # exact sum (float64 holds it), one rounding to fp32, then a true division: by a tensor,
+                # because torch's CUDA division by a Python number multiplies by its rounded reciprocal
                 x = t['x']
-                t['x'] = x.sum((2, 3)) / float(x.shape[2] * x.shape[3])
+                hw = torch.full((), float(x.shape[2] * x.shape[3]), dtype=torch.float32, device=x.device)
+                t['x'] = x.sum((2, 3), dtype=torch.float64).float() / hw
             elif op == 'flatten':
                 t['x'] = t['x'].flatten(1)
             elif op == 'copy':
@@ -258,7 +262,46 @@ class ModuleNet(nn.Module):
 
 
 # ------------------------------------------------------------------------------------------------ integer pipeline
-class IntPipeline:
+class _Pipeline:
+    """What both whole-network executors share: a static input buffer, a list of launches recorded
+    once, optional CUDA-graph replay, and the count of library kernels in one pass."""
+
+    @property
+    def n_launches(self):
+        """Kernels of this library in one pass, counted by the library itself while the pass was
+        recorded (a layer call can be several kernels: weight expansion, the convolution)."""
+        return len(self.calls) if self._n_launches is None else self._n_launches
+
+    def _capture(self):
+        with torch.cuda.device(self.device):
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._launch_all()  # warm-up outside capture: kernel attributes, weights expanded once
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = _ffi.lib().ds_launch_count()
+            with torch.cuda.graph(g):
+                self._launch_all()
+            self._n_launches = int(_ffi.lib().ds_launch_count() - before)  # kernels of one replay
+            self.graph = g
+
+    def run(self, x=None):
+        """x: fp32 CUDA tensor [batch, C, H, W] (copied into the static input buffer) or None to
+        reuse the buffer's contents.  Returns the static fp32 logits tensor."""
+        if x is not None:
+            self.x_in.copy_(x, non_blocking=True)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            before = _ffi.lib().ds_launch_count()
+            self._launch_all()
+            self._n_launches = int(_ffi.lib().ds_launch_count() - before)
+        return self.out
+
+
+class IntPipeline(_Pipeline):
     """Whole-network fixed-point executor.
 
     ``run(x)`` takes an fp32 CUDA batch of the fixed size given at construction and returns fp32
@@ -396,36 +439,170 @@ class IntPipeline:
                 _, xin, out, pad = c
                 out[:, pad:pad + xin.shape[1]].copy_(xin[:, :, ::2, ::2])
 
-    @property
-    def n_launches(self):
-        """Kernels of this library in one pass, counted by the library itself while the pass was
-        recorded (a layer call can be several kernels: weight expansion, the convolution)."""
-        return len(self.calls) if self._n_launches is None else self._n_launches
 
-    def _capture(self):
-        with torch.cuda.device(self.device):
-            s = torch.cuda.Stream()
-            s.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(s):
-                self._launch_all()  # warm-up outside capture: kernel attributes, weights expanded once
-            torch.cuda.current_stream().wait_stream(s)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            before = _ffi.lib().ds_launch_count()
-            with torch.cuda.graph(g):
-                self._launch_all()
-            self._n_launches = int(_ffi.lib().ds_launch_count() - before)  # kernels of one replay
-            self.graph = g
 
-    def run(self, x=None):
-        """x: fp32 CUDA tensor [batch, C, H, W] (copied into the static input buffer) or None to
-        reuse the buffer's contents.  Returns the static fp32 logits tensor."""
-        if x is not None:
-            self.x_in.copy_(x, non_blocking=True)
-        if self.graph is not None:
-            self.graph.replay()
-        else:
-            before = _ffi.lib().ds_launch_count()
-            self._launch_all()
-            self._n_launches = int(_ffi.lib().ds_launch_count() - before)
-        return self.out
+# ------------------------------------------------------------------------------------------------ staged pipeline
+class _Val:
+    """One activation tensor of the staged pipeline and the forms its readers need."""
+
+    def __init__(self, C, H, W):
+        self.C, self.H, self.W = C, H, W
+        self.halo = None        # not None: read by a convolution (needs the staged operand, this halo)
+        self.need_codes = False  # read as residual, by a pooling step or by the classifier
+        self.flat = False        # the result of global pooling: codes are [B,C]
+        self.zero_init = False   # codes are only partly written (option-A shortcut): start from zero
+        self.staged = None
+        self.codes = None        # int32 NHWC [B,H,W,C]; [B,C] after global pooling
+
+
+class StagedPipeline(_Pipeline):
+    """Whole-network fixed-point executor on staged activations: every convolution is the TMA-fed
+    kernel (``staged.conv2d``), activations travel between layers as the fp32 NHWC operand the next
+    convolution reads (clamped code + 0.5, physical halo) and, where a residual add, a pooling step
+    or the classifier needs them, as int32 NHWC codes.  ReLU, residual add, the fp32 rounding and
+    the next layer's quantiser clamp are fused into the convolution epilogues.  Same results as
+    ``IntPipeline`` and ``ModuleNet``, bit for bit.
+
+    Supports the steps of the ResNets (conv, maxpool, gap, linear after gap, copy, shortcutA);
+    networks that flatten a spatial map into a classifier (the MNIST ones) stay on ``IntPipeline``.
+    Needs act_integer_bits + act_fraction_bits <= 18 (the FP32-pipe bound) and right shifts only.
+    """
+
+    def __init__(self, net, weights, batch, device='cuda', use_graph=True):
+        from . import staged as S
+        self.S = S
+        self.net, self.batch, self.device = net, batch, torch.device(device)
+        self.I, self.F = net.act_integer_bits, net.act_fraction_bits
+        if utils.code_bits(self.I, self.F) > 18:
+            raise NotImplementedError("staged pipeline: activations wider than 18 bits")
+        self.packed, self.bias = [], []
+        for L, w in zip(net.layers, weights):
+            self.packed.append(utils.compress_bits(w['shift'].float(), w['sign'].float(), device=self.device))
+            self.bias.append((w['bias'] * (2 ** self.F)).int().to(self.device).contiguous())
+        self.x_in = torch.empty((batch,) + net.in_shape, dtype=torch.float32, device=self.device)
+        self.workspace = kernels.new_workspace(self.device)
+        self._plan()
+        self._n_launches = None
+        self.graph = None
+        if use_graph:
+            self._capture()
+
+    def _plan(self):
+        net, dev, B = self.net, self.device, self.batch
+        # pass 1: which forms of every tensor are read
+        C, H, W = net.in_shape
+        env = {'x': _Val(C, H, W)}
+        first = env['x']
+        vals, prog = [first], []
+        after_gap = False
+        for st in net.steps:
+            op = st[0]
+            if op == 'conv':
+                li, o = st[1], st[2]
+                L = net.layers[li]
+                src = env[o.get('src', 'x')]
+                src.halo = max(src.halo or 0, L.pad)
+                res = env[o['add']] if o.get('add') else None
+                if res is not None:
+                    res.need_codes = True
+                out = _Val(L.cout, (src.H + 2 * L.pad - L.k) // L.stride + 1, (src.W + 2 * L.pad - L.k) // L.stride + 1)
+                vals.append(out)
+                prog.append(('conv', li, src, res, out, bool(o.get('relu'))))
+                env[o.get('dst', 'x')] = out
+            elif op == 'maxpool':
+                _, k, s_, p_ = st
+                src = env['x']
+                src.need_codes = True
+                out = _Val(src.C, (src.H + 2 * p_ - k) // s_ + 1, (src.W + 2 * p_ - k) // s_ + 1)
+                vals.append(out)
+                prog.append(('maxpool', src, out, k, s_, p_))
+                env['x'] = out
+            elif op == 'gap':
+                src = env['x']
+                src.need_codes = True
+                out = _Val(src.C, 1, 1)
+                out.need_codes = out.flat = True
+                vals.append(out)
+                prog.append(('gap', src, out))
+                env['x'] = out
+                after_gap = True
+            elif op == 'linear':
+                if not after_gap:
+                    raise NotImplementedError("staged pipeline: a classifier on a flattened spatial map")
+                li, o = st[1], st[2]
+                src = env['x']
+                out = _Val(net.layers[li].cout, 1, 1)
+                vals.append(out)
+                prog.append(('linear', li, src, out, bool(o.get('relu'))))
+                env['x'] = out
+            elif op == 'copy':
+                env[st[2]] = env[st[1]]
+            elif op == 'shortcutA':
+                src = env[st[1]]
+                src.need_codes = True
+                pad = st[3] // 4
+                out = _Val(src.C + 2 * pad, (src.H + 1) // 2, (src.W + 1) // 2)
+                out.need_codes = out.zero_init = True
+                vals.append(out)
+                prog.append(('shortcutA', src, out, pad))
+                env[st[2]] = out
+            elif op == 'flatten':
+                if not after_gap:
+                    raise NotImplementedError("staged pipeline: flatten of a spatial map")
+            else:
+                raise NotImplementedError(op)
+        if first.need_codes or first.halo is None:
+            raise NotImplementedError("staged pipeline: the network input must feed a convolution only")
+        last = prog[-1]
+        if last[0] != 'linear' or sum(1 for q in prog if q[0] == 'linear') != 1:
+            raise NotImplementedError("staged pipeline: the last step must be the classifier")
+        # pass 2: buffers
+        for v in vals:
+            if v.halo is not None:
+                v.staged = self.S.StagedTensor(B, v.H, v.W, v.C, v.halo, dev)
+            if v.need_codes and v is not last[3]:
+                shape = (B, v.C) if v.flat else (B, v.H, v.W, v.C)
+                v.codes = (torch.zeros if v.zero_init else torch.empty)(shape, dtype=torch.int32, device=dev)
+        self.out = torch.empty((B, last[3].C), dtype=torch.float32, device=dev)
+        self.first = first
+        self.calls = [('stage',)] + prog
+
+    def _launch_all(self):
+        S, lib = self.S, _ffi.lib()
+        import ctypes
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        I, F = self.I, self.F
+        for c in self.calls:
+            op = c[0]
+            if op == 'stage':
+                rc = lib.ds_stage_nchw(self.x_in.data_ptr(), _ffi.IN_F32_CONV, I, F, ctypes.byref(self.first.staged.c),
+                                       stream)
+                _ffi.check(rc, "stage_nchw")
+            elif op == 'conv':
+                _, li, src, res, out, relu = c
+                L = self.net.layers[li]
+                S.conv2d(src.staged, L.weight_shape, self.bias[li], self.packed[li], L.stride, L.pad,
+                         act_integer_bits=I, act_fraction_bits=F, relu=relu, round_f32=True,
+                         residual=res.codes if res is not None else None, out_codes=out.codes, out_staged=out.staged,
+                         workspace=self.workspace)
+            elif op == 'maxpool':
+                _, src, out, k, s_, p_ = c
+                rc = lib.ds_maxpool_nhwc(src.codes.data_ptr(), self.batch, src.H, src.W, src.C, k, s_, p_,
+                                         out.codes.data_ptr() if out.codes is not None else None,
+                                         ctypes.byref(out.staged.c) if out.staged is not None else None, I, F, stream)
+                _ffi.check(rc, "maxpool_nhwc")
+            elif op == 'gap':
+                _, src, out = c
+                rc = lib.ds_avgpool_fix_nhwc(src.codes.data_ptr(), out.codes.data_ptr(), self.batch, src.H, src.W, src.C,
+                                             F, stream)
+                _ffi.check(rc, "avgpool_fix_nhwc")
+            elif op == 'linear':
+                _, li, src, out, relu = c
+                L, cw = self.net.layers[li], self.packed[li]
+                fuse = kernels._fuse(_ffi.IN_I32, _ffi.OUT_F32, I, F, relu=relu, workspace=self.workspace)
+                rc = lib.ds_linear_ex(src.codes.data_ptr(), cw.data.data_ptr(), self.bias[li].data_ptr(),
+                                      self.out.data_ptr(), self.batch, L.cin, L.cout, cw.bits, cw.base, fuse, stream)
+                _ffi.check(rc, "linear_ex")
+            elif op == 'shortcutA':
+                _, src, out, pad = c
+                out.codes[..., pad:pad + src.C].copy_(src.codes[:, ::2, ::2, :])

@@ -223,6 +223,80 @@ int ds_conv2d_prepare(const int32_t *packed, int B, int C, int H, int W, int OC,
                       long long *bytes_needed, void *stream);
 
 /*
+ * ---- Staged activations: the TMA-fed convolution path (no counterpart in the reference) ----------
+ *
+ * For a chain of shift layers (a whole network) the activations can stay in the form the FP32-pipe
+ * arithmetic reads and the tensor memory accelerator fetches: fp32 NHWC, value = code + 0.5, where
+ * code is the int32 fixed-point activation AFTER the quantiser clamp of the layer that will read it
+ * (round_to_fixed, utils.py:7-21, applied to a value already on the 2^-F grid), with `halo` pixels
+ * of 0.5 (the code 0) around every image and C rounded up to a multiple of 4 channels per pixel
+ * (the extra channels hold 0.5 too).  ds_staged_conv2d replaces F.pad + DEEP_SHIFT_CONV
+ * (kernels.py:32-53, shift.cu:399-669) on such a tensor: its input tiles come into shared memory
+ * through `cp.async.bulk.tensor` in im2col mode, so the im2col matrix exists neither in HBM nor in
+ * registers, and zero padding is the halo.  Results are bit-identical to ds_conv2d_ex.
+ *
+ * The caller owns every buffer.  A staged tensor must be filled with 0.5 once (ds_staged_fill)
+ * before its first use; the kernels only ever write its interior.
+ */
+typedef struct {
+    void *data;      /* fp32 [B][H + 2*halo][W + 2*halo][Cs], Cs = C rounded up to a multiple of 4; 16-byte aligned */
+    int B, H, W, C;  /* logical extent */
+    int halo;        /* >= the padding of every convolution that reads the tensor */
+} ds_staged_t;
+
+/* What ds_staged_conv2d writes; any subset of the four outputs.  v = acc + bias, then residual add
+ * (fp32 add of the two codes, as `out += identity` does), ReLU, fp32 rounding (round_f32). */
+typedef struct {
+    int32_t *codes;            /* [B][OH][OW][OC] int32 (NHWC): v                                   */
+    float *f32;                /* [B][OH][OW][OC] fp32: v / 2^F (modules.py:161-162)               */
+    void *nchw;                /* [B][OC][OH][OW]: v as int32, or v / 2^F as fp32 when nchw_is_f32 */
+    int nchw_is_f32;
+    const ds_staged_t *staged; /* operand of the next layer: clamp(v) + 0.5 with the clamp of I, F below
+                                  (geometry must be B, OH, OW, OC; any halo); may be NULL          */
+    const int32_t *residual;   /* [B][OH][OW][OC] int32 (NHWC) or NULL                             */
+    int relu, round_f32;
+    int act_integer_bits;      /* I and F of the quantiser of the layer that reads `staged`        */
+    int act_fraction_bits;     /* F: also the scale of f32 / nchw fp32 outputs                     */
+    int in_act_bits;           /* bound on the input: every staged value is code + 0.5 with
+                                  |code| <= 2^(in_act_bits-1); 1..18 (16 for 4.12 activations)     */
+    int reserved[3];
+} ds_staged_out_t;
+
+/* Bytes of a staged tensor of this geometry; -1 for bad arguments. */
+long long ds_staged_bytes(int B, int H, int W, int C, int halo);
+
+/* Writes 0.5 into every element (halo, padding channels and interior). */
+int ds_staged_fill(const ds_staged_t *t, void *stream);
+
+/* Quantises an NCHW tensor into the interior of a staged one.  in_kind: DS_IN_F32_CONV (fp32,
+ * round_to_fixed(x, I, F), utils.py:7-21 + modules.py:153), DS_IN_I32_CLAMP (int32 codes, the same
+ * quantiser applied to code / 2^F) or DS_IN_I32 (int32 codes taken as they are; |code| <= 2^17). */
+int ds_stage_nchw(const void *x, int in_kind, int act_integer_bits, int act_fraction_bits,
+                  const ds_staged_t *dst, void *stream);
+
+/* Expands the packed weights of one layer for ds_staged_conv2d (once per layer; depends on the
+ * weights, C, OC and the window only).  Call with prepared = NULL to get the size.  base must be 0. */
+int ds_staged_prepare(const int32_t *packed, int C, int OC, int KH, int KW, int bits, int base,
+                      void *prepared, long long prepared_bytes, long long *bytes_needed, void *stream);
+
+/* The convolution.  x->halo >= ph, pw.  `workspace` as ds_fuse_t.workspace (optional: lets the tiles
+ * after the last full wave of CTAs be shared along K); launches sharing one must not overlap. */
+int ds_staged_conv2d(const ds_staged_t *x, const void *prepared, long long prepared_bytes,
+                     const int32_t *bias, int OC, int KH, int KW, int sh, int sw, int ph, int pw,
+                     const ds_staged_out_t *out, void *workspace, long long workspace_bytes, void *stream);
+
+/* Max pooling of int32 NHWC codes [B][H][W][C] (square window k, stride, symmetric pad, as
+ * F.max_pool2d); writes int32 NHWC codes (may be NULL) and/or the staged operand of the next layer
+ * (clamp of I, F; may be NULL). */
+int ds_maxpool_nhwc(const int32_t *x, int B, int H, int W, int C, int k, int stride, int pad,
+                    int32_t *out_codes, const ds_staged_t *out_staged, int act_integer_bits,
+                    int act_fraction_bits, void *stream);
+
+/* Global average of int32 NHWC codes followed by the LinearShift entry conversion, as
+ * ds_avgpool_fix_i32; out [B][C] int32. */
+int ds_avgpool_fix_nhwc(const int32_t *x, int32_t *out, int B, int H, int W, int C, int F, void *stream);
+
+/*
  * Reads and clears the device-side flag that a kernel of this library sets when one of its
  * bounded waits ran out (its output is then undefined; it never happens in a correct run).
  * Synchronises the current device.  *flag = 0 means no error.

@@ -779,10 +779,11 @@ def test_residual_may_alias_the_output(oracle, cuda_device):
     ref = (ref.astype(np.float32) + res.astype(np.float32)).astype(np.int64).astype(np.int32)
     cw = _cw(shift, sign, cuda_device)
     counters = torch.zeros(16384, dtype=torch.int32, device=cuda_device)   # counters only: the atomics scheme
+    xd, bd = _t(x, cuda_device), _t(bias, cuda_device)
     for ws in (None, counters):
         buf = _t(res, cuda_device)
         f = kernels._fuse(_ffi.IN_I32_CLAMP, _ffi.OUT_I32, 4, 12, residual=buf, workspace=ws)
-        rc = _ffi.lib().ds_conv2d_ex(_t(x, cuda_device).data_ptr(), cw.data.data_ptr(), _t(bias, cuda_device).data_ptr(),
+        rc = _ffi.lib().ds_conv2d_ex(xd.data_ptr(), cw.data.data_ptr(), bd.data_ptr(),
                                      buf.data_ptr(), B, C, H, H, OC, 3, 3, 1, 1, 1, 1, cw.bits, cw.base, f,
                                      torch.cuda.current_stream(cuda_device).cuda_stream)
         assert rc == 0
@@ -833,12 +834,14 @@ def test_ps_module_repacks_when_parameters_change(oracle, cuda_device):
     assert not torch.equal(ya, yb)
     a.load_state_dict(b.state_dict())
     assert torch.equal(a(x), yb)
-    a.sign.data.neg_()                       # in place: the version counter moves
+    with torch.no_grad():
+        a.sign.neg_()                        # in place on the parameter: its version counter moves
     fresh = modules.Conv2dShift(8, 40, 3, padding=1, **kw).to(cuda_device)
     fresh.load_state_dict(a.state_dict())
     assert torch.equal(a(x), fresh(x)) and not torch.equal(a(x), yb)
     lin = modules.LinearShift(30, 70, **kw).to(cuda_device)
     xl = _t(rng.normal(0, 1, (65, 30)).astype(np.float32), cuda_device)
     y0 = lin(xl)
-    lin.shift.data.sub_(1.0)
+    with torch.no_grad():
+        lin.shift.sub_(1.0)
     assert not torch.equal(lin(xl), y0)
