@@ -503,24 +503,35 @@ def run_gemm(M, K, N, bits=5, dense=False, act_bits=16, iters=10, warmup=3, dev=
                 ms=ms, Tshift_ops_per_s=ops / ms / 1e9, GBps=nbytes / ms / 1e6)
 
 
-def run_conv(B, C, H, OC, k, stride, pad, bits=5, dense=False, act_bits=16, iters=10, warmup=3, dev="cuda"):
-    """One square shift convolution, same distributions, through `kernels.conv2d`."""
+def run_conv(B, C, H, OC, k, stride, pad, bits=5, dense=False, act_bits=16, iters=10, warmup=3, dev="cuda", staged=False):
+    """One square shift convolution, same distributions, through `kernels.conv2d` (int32 NCHW in and
+    out), or with `staged` through `staged.conv2d` (staged fp32 NHWC operand in, int32 NHWC codes and
+    the next layer's staged operand out: what a layer inside the staged pipeline does)."""
     import numpy as np
     import torch
-    from deepshift_b200 import kernels, utils
+    from deepshift_b200 import _ffi, kernels, utils
     rng = np.random.default_rng(20254)
     x = _sweep_acts(rng, (B, C, H, H)).to(dev)
     shift, sign = _sweep_weights(rng, (OC, C, k, k), bits, dense)
     cw = utils.compress_bits(shift, sign, device=torch.device(dev))
     shift_d = shift.to(dev)
-    ms = _time_launches(lambda: kernels.conv2d(x, shift_d, None, None, cw, (stride, stride), (pad, pad),
-                                               act_bits=act_bits), iters, warmup)
     OH = (H + 2 * pad - k) // stride + 1
+    if staged:
+        from deepshift_b200 import staged as S
+        xs = S.stage_nchw(x, 4, 12, pad, in_kind=_ffi.IN_I32)
+        codes = torch.empty((B, OH, OH, OC), dtype=torch.int32, device=dev)
+        nxt = S.StagedTensor(B, OH, OH, OC, 1, dev)
+        ms = _time_launches(lambda: S.conv2d(xs, (OC, C, k, k), None, cw, stride, pad, relu=True, round_f32=True,
+                                             out_codes=codes, out_staged=nxt), iters, warmup)
+    else:
+        ms = _time_launches(lambda: kernels.conv2d(x, shift_d, None, None, cw, (stride, stride), (pad, pad),
+                                                   act_bits=act_bits), iters, warmup)
     ops = B * OC * OH * OH * C * k * k
     num = 32 // (cw.bits + 1)
     nbytes = 4 * (B * C * H * H + OC * ((C * k * k + num - 1) // num) + B * OC * OH * OH)
     return dict(case="conv", B=B, C=C, H=H, OC=OC, k=k, stride=stride, pad=pad, weight_bits=bits, dense=dense,
-                field_bits=cw.bits, act_bits=act_bits, ms=ms, Tshift_ops_per_s=ops / ms / 1e9, GBps=nbytes / ms / 1e6)
+                field_bits=cw.bits, act_bits=act_bits, staged=staged, ms=ms, Tshift_ops_per_s=ops / ms / 1e9,
+                GBps=nbytes / ms / 1e6)
 
 
 def run_sweep(peak_fma, hbm_peak):
@@ -548,7 +559,7 @@ def run_case(args):
     if kind == "gemm" and len(dims) == 3:
         print(json.dumps(run_gemm(*dims, **kw)))
     elif kind == "conv" and len(dims) == 7:
-        print(json.dumps(run_conv(*dims, **kw)))
+        print(json.dumps(run_conv(*dims, staged=args.staged, **kw)))
     else:
         raise SystemExit("--case conv B C H OC K S P | --case gemm M K N")
 
@@ -567,6 +578,7 @@ def main():
     ap.add_argument("--bits", type=int, default=5)
     ap.add_argument("--dense", action="store_true")
     ap.add_argument("--act-bits", type=int, default=16)
+    ap.add_argument("--staged", action="store_true", help="--case conv: the TMA-fed kernel on a staged operand")
     args = ap.parse_args()
     if args.case:
         run_case(args)

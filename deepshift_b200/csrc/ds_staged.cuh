@@ -21,7 +21,7 @@ struct StagedDesc {
 };
 
 struct StagedConvParams {
-    const float* wt;      // prepared weights, [grid_n][ntiles][KQ][BN][4] floats (see prepare kernel)
+    const float* wt;      // prepared weights, [grid_n][ntiles][4*KQ][BN] floats (see the expand kernel)
     const int* negpre;    // [ntiles + 1][npad]: negative weights of a column in the k-tiles before t
     const int32_t* bias;  // [N] or null
     const int32_t* residual;  // [M][N] int32 codes (NHWC) or null
@@ -33,6 +33,7 @@ struct StagedConvParams {
     int out_nchw_f32;
     int os_H2, os_W2, os_Cs, os_halo;  // out_staged: rows and columns with halo, channels per pixel, halo
     int M, N, P, OH, OW;  // M = B * OH * OW output positions, P = OH * OW
+    unsigned inv_P, inv_OW;  // floor(2^32 / d): __umulhi(x, inv) is x / d or one less
     int sh, sw, KW;
     int cq_per_tap;       // channel groups of four per filter tap = Cs / 4
     int nkq;              // groups of four k in total = KH * KW * cq_per_tap

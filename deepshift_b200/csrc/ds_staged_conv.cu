@@ -15,9 +15,10 @@
 //   * k runs over (kh, kw, c) with c fastest (integer sums do not depend on the order of their
 //     terms, so the result is still bit-identical to the reference's (c, kh, kw) order).
 //
-// Shared-memory layout of a stage: A[kq][row][4] and B[kq][slot][4] floats, kq = group of four
-// consecutive k.  A consumer thread reads float4 = four k of one row / one column: 16 fragment
-// loads per 256 FFMAs, every load a conflict-free 128-byte (A) or broadcast 64-byte (B) access.
+// Shared-memory layout of a stage: A[kq][row][4] (kq = group of four consecutive k, as TMA delivers
+// it: four channels of a pixel are 16 contiguous bytes) and B[k][column] floats.  A consumer
+// thread holds four rows x four k of A (four float4) and, per k, eight columns of B (two float4):
+// 24 fragment loads per 256 FFMAs, every load a conflict-free 128-byte or broadcast 64-byte access.
 //
 // Roles: 16 consumer warps (8 x 8 outputs per thread: 256 x 128 tile, or 512 x 64 for layers with
 // at most 64 output channels) and one producer warp whose lane 0 issues the copies.  STAGES-deep
@@ -241,30 +242,31 @@ __global__ void __launch_bounds__(ST_NT, 1) staged_conv_kernel(const __grid_cons
             const int s = git % STAGES;
             if (!st_mbar_wait(bar_full + 8 * s, unsigned(git / STAGES) & 1u, bad)) bad = true;
             const float4* sa = reinterpret_cast<const float4*>(gbase + s * C::STAGE_BYTES) + tm;
-            const float4* sb = reinterpret_cast<const float4*>(gbase + s * C::STAGE_BYTES + C::A_BYTES) + tn;
-            auto kq_step = [&](int kq) {
-                float4 b[TN];
+            const float* sb = reinterpret_cast<const float*>(gbase + s * C::STAGE_BYTES + C::A_BYTES) + 4 * tn;
+            const int nq = min(KQ, p.nkq - (cur.t_begin + it) * KQ);  // groups of this tile that hold data
 #pragma unroll
-                for (int j = 0; j < TN; ++j) b[j] = sb[kq * BN + j * TNG];
+            for (int kq = 0; kq < KQ; ++kq) {
+                if (kq < nq) {
 #pragma unroll
-                for (int i = 0; i < kTM; ++i) {
-                    const float4 a = sa[kq * BM + i * TMG];
+                    for (int h = 0; h < 2; ++h) {
+                        float4 a[4];
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a.x, b[j].x, accf[i][j]);
+                        for (int i = 0; i < 4; ++i) a[i] = sa[kq * BM + (4 * h + i) * TMG];
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a.y, b[j].y, accf[i][j]);
+                        for (int kk = 0; kk < 4; ++kk) {
+                            float b[TN];
+                            *reinterpret_cast<float4*>(&b[0]) = *reinterpret_cast<const float4*>(sb + (kq * 4 + kk) * BN);
+                            *reinterpret_cast<float4*>(&b[4]) =
+                                *reinterpret_cast<const float4*>(sb + (kq * 4 + kk) * BN + BN / 2);
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a.z, b[j].z, accf[i][j]);
+                            for (int i = 0; i < 4; ++i) {
+                                const float av = kk == 0 ? a[i].x : (kk == 1 ? a[i].y : (kk == 2 ? a[i].z : a[i].w));
 #pragma unroll
-                    for (int j = 0; j < TN; ++j) accf[i][j] = __fmaf_rd(a.w, b[j].w, accf[i][j]);
+                                for (int j = 0; j < TN; ++j) accf[4 * h + i][j] = __fmaf_rd(av, b[j], accf[4 * h + i][j]);
+                            }
+                        }
+                    }
                 }
-            };
-            const int nq = p.nkq - (cur.t_begin + it) * KQ;  // groups of this tile that hold data
-            if (nq >= KQ) {
-#pragma unroll
-                for (int kq = 0; kq < KQ; ++kq) kq_step(kq);
-            } else {
-                for (int kq = 0; kq < nq; ++kq) kq_step(kq);
             }
             __syncwarp();
             if (lane == 0) st_mbar_arrive(bar_empty + 8 * s);
@@ -293,24 +295,25 @@ __global__ void __launch_bounds__(ST_NT, 1) staged_conv_kernel(const __grid_cons
 
         // ---- epilogue --------------------------------------------------------------------------
         // thread (tm, tn): rows m0 + i*TMG + tm, columns n0 + (j/4)*(BN/2) + 4*tn + (j%4)
-        auto ncol = [&](int j) { return (j >> 2) * (BN / 2) + 4 * tn + (j & 3); };
-        auto part = [&](int i, int j) -> int { return accs[(i * TN + j) * ST_CONS + t] - ndrains * kMagicBits; };
-        int corr[TN];
+        int addc[TN];  // per column: negative-weight correction of this K range, and (below) the bias
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
-            const int* np = p.negpre + cur.n0 + ncol(j);
-            corr[j] = __ldg(np + (size_t)cur.t_end * p.npad) - __ldg(np + (size_t)cur.t_begin * p.npad);
+            const int* np = p.negpre + cur.n0 + (j >> 2) * (BN / 2) + 4 * tn + (j & 3);
+            addc[j] = __ldg(np + (size_t)cur.t_end * p.npad) - __ldg(np + (size_t)cur.t_begin * p.npad) -
+                      ndrains * kMagicBits;
         }
         bool finish_tile = true;
-        const int* sums = nullptr;  // tail tiles: partial sums of all splits in the workspace
         if (cur.tail_idx >= 0) {
+            // Tail split: every CTA of the tile leaves its partial sums in the workspace; the one that
+            // arrives last at the tile's counter adds them up, each thread its own outputs, and goes on.
             constexpr int SLOT = kTM * TN * ST_CONS;
             int* basep = p.partials + (size_t)cur.tail_idx * p.tail_splits * SLOT;
             int* mine = basep + (size_t)cur.sp * SLOT;
 #pragma unroll
-            for (int j = 0; j < TN; ++j)
+            for (int i = 0; i < kTM; ++i)
 #pragma unroll
-                for (int i = 0; i < kTM; ++i) __stcg(mine + (i * TN + j) * ST_CONS + t, part(i, j) + corr[j]);
+                for (int j = 0; j < TN; ++j)
+                    __stcg(mine + (i * TN + j) * ST_CONS + t, accs[(i * TN + j) * ST_CONS + t] + addc[j]);
             __threadfence();
             st_consumer_bar();
             if (t == 0) {
@@ -322,87 +325,108 @@ __global__ void __launch_bounds__(ST_NT, 1) staged_conv_kernel(const __grid_cons
             }
             st_consumer_bar();
             finish_tile = flags[0] != 0;
-            if (finish_tile) __threadfence();
-            sums = basep;
             st_consumer_bar();  // flags[0] is rewritten by the next tail item
+            if (finish_tile) {
+                __threadfence();
+                // totals back into this thread's slots, so that the code below serves both cases
+#pragma unroll
+                for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                    for (int j = 0; j < TN; ++j) {
+                        int a = 0;
+                        for (int q = 0; q < p.tail_splits; ++q)
+                            a += __ldcg(basep + (size_t)q * SLOT + (i * TN + j) * ST_CONS + t);
+                        accs[(i * TN + j) * ST_CONS + t] = a;
+                    }
+#pragma unroll
+                for (int j = 0; j < TN; ++j) addc[j] = 0;
+            }
         }
         if (finish_tile) {
-            int addc[TN];
+            if (p.bias) {
 #pragma unroll
-            for (int j = 0; j < TN; ++j) {
-                const int n = cur.n0 + ncol(j);
-                addc[j] = (n < p.N && p.bias) ? __ldg(p.bias + n) : 0;
-                if (!sums) addc[j] += corr[j];
+                for (int j = 0; j < TN; ++j) {
+                    const int n = cur.n0 + (j >> 2) * (BN / 2) + 4 * tn + (j & 3);
+                    if (n < p.N) addc[j] += __ldg(p.bias + n);
+                }
             }
-#pragma unroll
+            const bool vec = (p.N & 3) == 0;  // then a group of four columns is inside N or outside it
+            const bool need_pix = p.out_staged || p.out_nchw;
+#pragma unroll 1
             for (int i = 0; i < kTM; ++i) {
                 const int m = cur.m0 + i * TMG + tm;
-                if (m >= p.M) continue;
-                int b = 0, oh = 0, ow = 0;
-                if (p.out_staged || p.out_nchw) {
-                    b = m / p.P;
-                    const int pp = m - b * p.P;
-                    oh = pp / p.OW;
+                if (m >= p.M) break;
+                int b = 0, pp = 0, oh = 0, ow = 0;
+                if (need_pix) {
+                    // m = (b, oh, ow); floor(2^32/d) multipliers are at most one short of the quotient
+                    b = int(__umulhi(unsigned(m), p.inv_P));
+                    pp = m - b * p.P;
+                    if (pp >= p.P) { pp -= p.P; ++b; }
+                    oh = int(__umulhi(unsigned(pp), p.inv_OW));
                     ow = pp - oh * p.OW;
+                    if (ow >= p.OW) { ow -= p.OW; ++oh; }
                 }
+                const size_t orow = (size_t)m * p.N;
+                const size_t srow = need_pix && p.out_staged
+                    ? (((size_t)b * p.os_H2 + oh + p.os_halo) * p.os_W2 + ow + p.os_halo) * p.os_Cs : 0;
 #pragma unroll
                 for (int h = 0; h < TN / 4; ++h) {
-                    const int n = cur.n0 + ncol(4 * h);
+                    const int n = cur.n0 + h * (BN / 2) + 4 * tn;
                     if (n >= p.N) continue;
-                    const size_t o = (size_t)m * p.N + n;
-                    const bool vec = (p.N % 4 == 0);  // then n + 3 < N as well
                     int v[4];
-                    int r4[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] = accs[(i * TN + 4 * h + e) * ST_CONS + t] + addc[4 * h + e];
                     if (p.residual) {
+                        int r4[4] = {0, 0, 0, 0};
                         if (vec) {
-                            const int4 r = __ldg(reinterpret_cast<const int4*>(p.residual + o));
+                            const int4 r = __ldg(reinterpret_cast<const int4*>(p.residual + orow + n));
                             r4[0] = r.x; r4[1] = r.y; r4[2] = r.z; r4[3] = r.w;
                         } else {
 #pragma unroll
                             for (int e = 0; e < 4; ++e)
-                                if (n + e < p.N) r4[e] = __ldg(p.residual + o + e);
+                                if (n + e < p.N) r4[e] = __ldg(p.residual + orow + n + e);
                         }
-                    }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int j = 4 * h + e;
-                        int a;
-                        if (sums) {
-                            a = 0;
-                            for (int q = 0; q < p.tail_splits; ++q)
-                                a += __ldcg(sums + (size_t)q * (kTM * TN * ST_CONS) + (i * TN + j) * ST_CONS + t);
-                        } else {
-                            a = part(i, j);
-                        }
-                        a += addc[j];
                         // fp32 add of the two values as the reference's `out += identity` does it
-                        if (p.residual) a = __float2int_rn(__int2float_rn(a) + __int2float_rn(r4[e]));
-                        if (p.relu) a = max(a, 0);
-                        if (p.round_f32) a = __float2int_rn(__int2float_rn(a));
-                        v[e] = a;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = __float2int_rn(__int2float_rn(v[e]) + __int2float_rn(r4[e]));
+                    }
+                    if (p.relu) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = max(v[e], 0);
+                    }
+                    if (p.round_f32) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) v[e] = __float2int_rn(__int2float_rn(v[e]));
                     }
                     if (p.out_codes) {
-                        if (vec) *reinterpret_cast<int4*>(p.out_codes + o) = make_int4(v[0], v[1], v[2], v[3]);
-                        else
+                        if (vec) {
+                            *reinterpret_cast<int4*>(p.out_codes + orow + n) = make_int4(v[0], v[1], v[2], v[3]);
+                        } else {
+#pragma unroll
                             for (int e = 0; e < 4; ++e)
-                                if (n + e < p.N) p.out_codes[o + e] = v[e];
+                                if (n + e < p.N) p.out_codes[orow + n + e] = v[e];
+                        }
                     }
                     if (p.out_f32) {
-                        if (vec)
-                            *reinterpret_cast<float4*>(p.out_f32 + o) =
+                        if (vec) {
+                            *reinterpret_cast<float4*>(p.out_f32 + orow + n) =
                                 make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
                                             __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
-                        else
+                        } else {
+#pragma unroll
                             for (int e = 0; e < 4; ++e)
-                                if (n + e < p.N) p.out_f32[o + e] = __int2float_rn(v[e]) * p.inv_scale;
+                                if (n + e < p.N) p.out_f32[orow + n + e] = __int2float_rn(v[e]) * p.inv_scale;
+                        }
                     }
                     if (p.out_nchw) {
+                        const size_t on = ((size_t)b * p.N + n) * p.P + pp;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             if (n + e >= p.N) continue;
-                            const size_t on = ((size_t)b * p.N + n + e) * p.P + (size_t)oh * p.OW + ow;
-                            if (p.out_nchw_f32) static_cast<float*>(p.out_nchw)[on] = __int2float_rn(v[e]) * p.inv_scale;
-                            else static_cast<int*>(p.out_nchw)[on] = v[e];
+                            if (p.out_nchw_f32)
+                                static_cast<float*>(p.out_nchw)[on + (size_t)e * p.P] = __int2float_rn(v[e]) * p.inv_scale;
+                            else
+                                static_cast<int*>(p.out_nchw)[on + (size_t)e * p.P] = v[e];
                         }
                     }
                     if (p.out_staged) {
@@ -410,11 +434,11 @@ __global__ void __launch_bounds__(ST_NT, 1) staged_conv_kernel(const __grid_cons
                         float f[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int c = min(max(v[e], p.rq_lo), p.rq_hi) * p.rq_mul + p.rq_add;
+                            int c = min(max(v[e], p.rq_lo), p.rq_hi);
+                            if (p.rq_mul != 1) c = c * p.rq_mul + p.rq_add;
                             f[e] = (n + e < p.N) ? (__int2float_rn(c) + 0.5f) : 0.5f;
                         }
-                        const size_t os = (((size_t)b * p.os_H2 + oh + p.os_halo) * p.os_W2 + ow + p.os_halo) * p.os_Cs + n;
-                        *reinterpret_cast<float4*>(p.out_staged + os) = make_float4(f[0], f[1], f[2], f[3]);
+                        *reinterpret_cast<float4*>(p.out_staged + srow + n) = make_float4(f[0], f[1], f[2], f[3]);
                     }
                 }
             }
@@ -424,43 +448,35 @@ __global__ void __launch_bounds__(ST_NT, 1) staged_conv_kernel(const __grid_cons
 }
 
 // Expands packed weights into the layout the kernel copies per k-tile:
-//   wt[nt][t][kq][slot][e] = weight(n, k'),  n = nt*BN + (slot / TNG / 4)*(BN/2) + 4*(slot % TNG) + (slot / TNG) % 4,
-//   k' = (t*KQ + kq)*4 + e = tap * Cs + c  (tap = kh*KW + kw), the reference's k being c*KH*KW + tap;
-// 0 for c >= C, tap >= KH*KW, n >= N and zero weights.  negcnt[t][n] counts the negative ones.
+//   wt[nt][t][kl][nl] = weight(n = nt*BN + nl, k' = t*4*KQ + kl),  k' = tap * Cs + c  (tap = kh*KW + kw),
+// the reference's k being c*KH*KW + tap; 0 for c >= C, tap >= KH*KW, n >= N and zero weights.
+// negcnt[t][n] counts the negative ones.  One thread per (k-tile, column).
 template <int BN>
 __global__ void __launch_bounds__(256) staged_expand_kernel(const int32_t* __restrict__ packed, Decode dec, int C, int Cs,
-                                                            int taps, int N, int K, int ntiles, int npad,
+                                                            int taps, int N, int ntiles, int npad,
                                                             float* __restrict__ wt, int* __restrict__ negcnt)
 {
-    using Cf = StCfg<BN>;
-    constexpr int KQ = Cf::KQ, TNG = Cf::TNG;
+    constexpr int KT = 4 * StCfg<BN>::KQ;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // (tile, n)
     if (idx >= (long long)ntiles * npad) return;
     const int tl = int(idx / npad), n = int(idx - (long long)tl * npad);
     const int nt = n / BN, nl = n - nt * BN;
-    // column nl of the tile sits in slot j*TNG + tn with nl = (j/4)*(BN/2) + 4*tn + j%4
-    const int hi = nl / (BN / 2), rem = nl - hi * (BN / 2);
-    const int tn = rem / 4, j = hi * 4 + (rem & 3);
-    const int slot = j * TNG + tn;
     const uint32_t fmask = (1u << dec.fw) - 1u;
-    float* dst = wt + ((size_t)nt * ntiles + tl) * (KQ * BN * 4) + slot * 4;
+    float* dst = wt + ((size_t)nt * ntiles + tl) * (KT * BN) + nl;
     int negs = 0;
-    for (int kq = 0; kq < KQ; ++kq) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        float* pv = &v.x;
-        for (int e = 0; e < 4; ++e) {
-            const int kp = (tl * KQ + kq) * 4 + e;
-            const int tap = kp / Cs, c = kp - tap * Cs;
-            if (n < N && tap < taps && c < C) {
-                const int k = c * taps + tap;
-                const int word = k / dec.num, sl = k - word * dec.num;
-                const uint32_t w = uint32_t(__ldg(packed + (size_t)n * dec.row_len + word));
-                int neg;
-                pv[e] = decode_f32((w >> (sl * dec.fw)) & fmask, dec, true, neg);
-                negs += neg;
-            }
+    for (int kl = 0; kl < KT; ++kl) {
+        const int kp = tl * KT + kl;
+        const int tap = kp / Cs, c = kp - tap * Cs;
+        float v = 0.f;
+        if (n < N && tap < taps && c < C) {
+            const int k = c * taps + tap;
+            const int word = k / dec.num, sl = k - word * dec.num;
+            const uint32_t w = uint32_t(__ldg(packed + (size_t)n * dec.row_len + word));
+            int neg;
+            v = decode_f32((w >> (sl * dec.fw)) & fmask, dec, true, neg);
+            negs += neg;
         }
-        *reinterpret_cast<float4*>(dst + (size_t)kq * BN * 4) = v;
+        dst[(size_t)kl * BN] = v;
     }
     negcnt[idx] = negs;
 }
@@ -646,9 +662,9 @@ extern "C" int ds_staged_prepare(const int32_t* packed, int C, int OC, int KH, i
     const long long threads = (long long)g.ntiles * g.npad;
     const unsigned blocks = unsigned((threads + 255) / 256);
     if (g.BN == 128)
-        staged_expand_kernel<128><<<blocks, 256, 0, st>>>(packed, dec, C, Cs, taps, OC, int(K), g.ntiles, g.npad, wt, negcnt);
+        staged_expand_kernel<128><<<blocks, 256, 0, st>>>(packed, dec, C, Cs, taps, OC, g.ntiles, g.npad, wt, negcnt);
     else
-        staged_expand_kernel<64><<<blocks, 256, 0, st>>>(packed, dec, C, Cs, taps, OC, int(K), g.ntiles, g.npad, wt, negcnt);
+        staged_expand_kernel<64><<<blocks, 256, 0, st>>>(packed, dec, C, Cs, taps, OC, g.ntiles, g.npad, wt, negcnt);
     staged_prefix_kernel<<<(g.npad + 127) / 128, 128, 0, st>>>(negcnt, negpre, g.ntiles, g.npad);
     note_launch(2);
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
@@ -696,6 +712,8 @@ extern "C" int ds_staged_conv2d(const ds_staged_t* x, const void* prepared, long
     p.relu = out->relu;
     p.round_f32 = out->round_f32;
     p.inv_scale = 1.0f / float(1ll << F);
+    p.inv_P = p.P == 1 ? 0xFFFFFFFFu : unsigned((1ull << 32) / unsigned(p.P));
+    p.inv_OW = OW == 1 ? 0xFFFFFFFFu : unsigned((1ull << 32) / unsigned(OW));
     // Terms between drains: every staged value is code + 0.5 with |code| <= 2^(ab-1).
     const int ab = out->in_act_bits;
     if (ab < 1 || ab > 18) return DS_ERR_UNSUPPORTED;
