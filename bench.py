@@ -233,7 +233,7 @@ def run_ours(args, rank, world, local):
     B = BATCH_PER_GPU
     x_host = W.make_input(net, B, rank=rank).pin_memory()
     x_dev = x_host.to(dev)
-    pipe = W.StagedPipeline(net, ws, B, dev, use_graph=True)
+    pipe = W.IntPipeline(net, ws, B, dev, use_graph=True)
     gathered = torch.empty((world * B, net.layers[-1].cout), dtype=torch.float32, device=dev) if world > 1 else None
 
     def step():
@@ -324,7 +324,7 @@ def run_ours(args, rank, world, local):
     # roofline of the dominant kernel: the 3x3 convolutions on the warp-specialised FP32-pipe kernel
     roofline = sweep = None
     if rank == 0:
-        nograph = W.StagedPipeline(net, ws, B, dev, use_graph=False)
+        nograph = W.IntPipeline(net, ws, B, dev, use_graph=False)
         nograph.x_in.copy_(x_dev)
         shapes = W._trace_shapes(net)
         per_layer, all_calls = {}, []
@@ -345,9 +345,9 @@ def run_ours(args, rank, world, local):
                 continue
             for c, a, b in evs:
                 if c[0] in ("conv", "linear"):
-                    per_layer.setdefault(c[1], []).append(a.elapsed_time(b))
+                    per_layer.setdefault(c[2], []).append(a.elapsed_time(b))
                 if rep == reps:
-                    all_calls.append((c[0], c[1] if c[0] in ("conv", "linear") else None, a.elapsed_time(b)))
+                    all_calls.append((c[0], c[2] if c[0] in ("conv", "linear") else None, a.elapsed_time(b)))
         dom_ops = dom_ms = dom_bytes = 0.0
         dom_n = 0
         for li, times in per_layer.items():
@@ -445,7 +445,7 @@ def check_parity(net, ws, pipe, model, x_dev, cpu_x, cpu_logits, cpu_kind, dev):
         # only the convolution kernel has the quirk; the linear kernel skips zero signs (shift_cpu.cpp:190-201)
         quirk = [dict(w, sign=torch.where(w['sign'] == 0, torch.ones_like(w['sign']), w['sign']))
                  if L.kind == 'conv' else w for L, w in zip(net.layers, ws)]
-        got = W.StagedPipeline(net, quirk, n, dev, use_graph=False).run(xs.to(dev)).cpu().numpy()
+        got = W.IntPipeline(net, quirk, n, dev, use_graph=False).run(xs.to(dev)).cpu().numpy()
         out["reference_binary"] = bool(np.array_equal(got, cpu_logits[:n]))
     return out
 
