@@ -470,14 +470,28 @@ def _sweep_acts(rng, shape):
 
 
 def _time_launches(fn, iters, warmup=3):
+    """Average device time of one call of `fn`: `iters` calls captured into one CUDA graph (so that the
+    host's launch path, tens of microseconds per call from Python, is not what gets timed for small
+    layers), replayed once to warm up and once between CUDA events."""
     import torch
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        fn()   # allocations of the stream's own workspace happen before capture
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(iters):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(iters):
-        fn()
+    graph.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters

@@ -373,16 +373,19 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     };
 
     // ---- main loop: two shared buffers, register prefetch, one barrier per tile --------------
-    fill_ktab(0, 0);
+    // gridDim.z > 1 (integer path, plain epilogue only): CTA z takes k-tiles [t_begin, t_end)
+    const int t_begin = blockIdx.z * p.tiles_per_split;
+    const int t_end = min(p.ntiles, t_begin + p.tiles_per_split);
+    fill_ktab(t_begin, 0);
     __syncthreads();
-    fetch(0, 0);
-    fill_ktab(1, 1);
-    stash(0, 0);
+    fetch(t_begin, 0);
+    fill_ktab(t_begin + 1, 1);
+    stash(t_begin, 0);
     __syncthreads();
     int since = 0;
-    for (int tile = 0; tile < p.ntiles; ++tile) {
-        const int buf = tile & 1;
-        const bool more = tile + 1 < p.ntiles;
+    for (int tile = t_begin; tile < t_end; ++tile) {
+        const int buf = (tile - t_begin) & 1;
+        const bool more = tile + 1 < t_end;
         if (more) fetch(tile + 1, buf ^ 1);
         compute(buf);
         if (FP && ++since == p.flush_tiles) {
@@ -398,6 +401,13 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     if (FP) drain();  // each thread reads back only its own slots below
 
     // ---- epilogue -----------------------------------------------------------------------------
+    if (!FP && gridDim.z > 1) {
+        // split along K: integer adds into the zeroed output commute, the bias goes in once
+        reduce_tile<TN, CONV>(
+            p, m0, n0, tm, tn, BM, BN, [&](int i, int j, long long) -> int { return acc[FP ? 0 : i][FP ? 0 : j]; },
+            [&](int col) -> int { return (blockIdx.z == 0 && p.bias && n0 + col < p.N) ? __ldg(p.bias + n0 + col) : 0; });
+        return;
+    }
     store_tile<TN, CONV>(
         p, m0, n0, tm, tn, BM, BN,
         [&](int i, int j, long long) -> int {
@@ -457,7 +467,19 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     }
     const long long gx = ((long long)p.M + BM - 1) / BM, gy = (p.N + BN - 1) / BN;
     if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
-    kern<<<dim3((unsigned)gx, (unsigned)gy), NT, smem, st>>>(p);
+    p.splits = 1;
+    p.tiles_per_split = p.ntiles;
+    const bool plain = p.out_kind == DS_OUT_I32 && !p.relu && !p.requant && !p.round_f32 && !p.residual && !p.operand_out;
+    if (MODE == MODE_INT && AM == AM_LINEAR && plain && gx * gy < 148) {
+        // Few output tiles (small batch): split K across gridDim.z until two CTAs per SM have work;
+        // the partial sums meet through integer atomics in the zeroed output.
+        int splits = 1;
+        while (splits < 16 && gx * gy * splits < 2 * 148 && p.ntiles / (splits * 2) >= 4) splits *= 2;
+        p.tiles_per_split = (p.ntiles + splits - 1) / splits;
+        p.splits = (p.ntiles + p.tiles_per_split - 1) / p.tiles_per_split;
+        if (p.splits > 1 && cudaMemsetAsync(p.out, 0, size_t(p.M) * size_t(p.N) * 4, st) != cudaSuccess) return DS_ERR_CUDA;
+    }
+    kern<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)p.splits), NT, smem, st>>>(p);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
@@ -654,9 +676,16 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     if (p.residual && (reinterpret_cast<uintptr_t>(p.residual) & 3u)) return DS_ERR_ALIGN;
     p.prepared = nullptr;  // weights expanded ahead of time exist for convolutions only
     p.prepared_bytes = 0;
-    // the small-batch kernel computes on the integer pipe and has a single output
-    if (M <= 64 && p.in_kind != DS_IN_OPERAND_F32 && !p.operand_out)
-        return launch_small_linear(p, static_cast<cudaStream_t>(stream));
+    // Small batches run on the integer pipe: up to 16 rows on the kernel that splits K across the
+    // lanes of a warp, up to 64 rows on the block kernel with a 64-row tile (K split across CTAs
+    // when nothing is fused into the epilogue).
+    if (p.in_kind != DS_IN_OPERAND_F32 && !p.operand_out) {
+        if (M <= 16) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
+        if (M <= 64) {
+            const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_INT, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
+            if (rc != DS_ERR_UNSUPPORTED) return rc;
+        }
+    }
     return launch_am<AM_LINEAR>(p, fp, static_cast<cudaStream_t>(stream));
 }
 

@@ -50,7 +50,9 @@ def test_compress_api_matches_reference_signature(oracle, cuda_device):
 
 # ----------------------------------------------------------------------------------------- linear
 LINEAR_SHAPES = [(1, 1, 1), (3, 7, 5), (64, 784, 512), (130, 131, 129), (257, 500, 10), (64, 512, 10), (200, 96, 70),
-                 (1000, 300, 40), (1, 4096, 33), (513, 29, 260)]
+                 (1000, 300, 40), (1, 4096, 33), (513, 29, 260),
+                 (1, 4096, 4096), (64, 4096, 4096),     # the small-batch corner of the shift-GEMM sweep
+                 (2, 640, 37), (5, 1031, 300), (8, 512, 1000), (13, 2048, 24), (16, 96, 4100), (17, 520, 130), (40, 3000, 70)]
 
 
 @pytest.mark.parametrize("M,K,N", LINEAR_SHAPES)
@@ -875,3 +877,22 @@ def test_conv_reads_and_writes_fp32_operands(oracle, cuda_device, shape):
     with pytest.raises(RuntimeError):   # the operand form exists for the FP32-pipe path only
         kernels.conv2d_fused(opnd_in, (OC, C, k, k), _t(bias, cuda_device), cw, s, p, in_kind=_ffi.IN_OPERAND_F32,
                              act_integer_bits=16, act_fraction_bits=16)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 23, 64])
+def test_small_batch_linear_with_fused_epilogue(oracle, cuda_device, M):
+    """Small batches (the kernels that split K across lanes / across CTAs) with everything fused:
+    LinearShift's fp32 entry conversion on read, residual add, ReLU, fp32 output."""
+    from deepshift_b200 import _ffi, kernels
+    rng = np.random.default_rng(600 + M)
+    K, N, F = 515, 130, 12
+    xf = rng.normal(0, 4, (M, K)).astype(np.float32)
+    shift, sign = weights(rng, (N, K))
+    bias = rng.integers(-2000, 2000, N).astype(np.int32)
+    res = rng.integers(-50000, 50000, (M, N)).astype(np.int32)
+    acc = oracle.linear(oracle.to_fixed_linear(xf, F), shift, sign, bias)
+    ref = np.maximum(acc.astype(np.float32) + res.astype(np.float32), 0).astype(np.int64).astype(np.int32)
+    out = kernels.linear_fused(_t(xf, cuda_device), N, _t(bias, cuda_device), _cw(shift, sign, cuda_device),
+                               in_kind=_ffi.IN_F32_LINEAR, out_kind=_ffi.OUT_F32, act_integer_bits=4,
+                               act_fraction_bits=F, relu=True, residual=_t(res, cuda_device))
+    assert np.array_equal(out.cpu().numpy(), oracle.from_fixed(ref, F))
