@@ -896,3 +896,41 @@ def test_small_batch_linear_with_fused_epilogue(oracle, cuda_device, M):
                                in_kind=_ffi.IN_F32_LINEAR, out_kind=_ffi.OUT_F32, act_integer_bits=4,
                                act_fraction_bits=F, relu=True, residual=_t(res, cuda_device))
     assert np.array_equal(out.cpu().numpy(), oracle.from_fixed(ref, F))
+
+
+def test_reference_binding_stub_against_the_library(oracle, cuda_device):
+    """deepshift_b200/reference_binding/deepshift_cuda.py, the module a maintainer of the reference
+    tree puts in place of the pybind extension: its three functions, called the way
+    deepshift/kernels/kernels.py:10-74 calls them (zeroed outputs, input padded with F.pad, a zero
+    bias when there is none), reproduce the oracle."""
+    import importlib.util
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "deepshift_b200",
+                        "reference_binding", "deepshift_cuda.py")
+    spec = importlib.util.spec_from_file_location("deepshift_cuda_stub", path)
+    stub = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(stub)
+    rng = np.random.default_rng(808)
+    # COMPRESS_SIGN_SHIFT as utils.py:74-86 / kernels.py:69-74 use it
+    OC, C, k = 37, 6, 3
+    shift, sign = weights(rng, (OC, C, k, k), zeros=False)
+    bits, num = 4, 6
+    row = (C * k * k + num - 1) // num
+    packed = torch.zeros([row * OC], dtype=torch.int32, device=cuda_device)
+    stub.COMPRESS_SIGN_SHIFT(_t(-shift, cuda_device), _t(sign, cuda_device), packed, 0, bits, OC, C, k, k, row, num)
+    assert np.array_equal(packed.cpu().numpy().reshape(OC, row), oracle.compress(-shift.reshape(OC, -1), sign.reshape(OC, -1), bits, 0))
+    # DEEP_SHIFT_CONV on the tensor kernels.py:32-36 has padded
+    x = acts_wide(rng, (2, C, 9, 11), 20)
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    xp = torch.nn.functional.pad(_t(x, cuda_device), (1, 1, 1, 1), mode='constant', value=0)
+    out = torch.zeros([2, OC, (xp.size(2) - k) // 2 + 1, (xp.size(3) - k) // 2 + 1], dtype=torch.int32, device=cuda_device)
+    stub.DEEP_SHIFT_CONV(xp, packed, _t(bias, cuda_device), out, (2, 2), (1, 1, 1, 1), k, k, 0, bits)
+    assert np.array_equal(out.cpu().numpy(), oracle.conv2d(x, shift, sign, bias, (2, 2), (1, 1)))
+    # DEEP_SHIFT_LINEAR
+    M, K, N = 70, 131, 29
+    xl = acts_wide(rng, (M, K), 24)
+    sl, gl = weights(rng, (N, K))
+    cw = _cw(sl, gl, cuda_device)
+    outl = torch.zeros([M, N], dtype=torch.int32, device=cuda_device)
+    zero_bias = torch.zeros([N], dtype=torch.int32, device=cuda_device)
+    stub.DEEP_SHIFT_LINEAR(_t(xl, cuda_device), cw.data, zero_bias, outl, cw.base, cw.bits, N)
+    assert np.array_equal(outl.cpu().numpy(), oracle.linear(xl, sl, gl, None))

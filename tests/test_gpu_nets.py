@@ -62,3 +62,20 @@ def test_resnet18_benchmark_batch_properties(cuda_device):
     small = W.IntPipeline(net, ws, 8, cuda_device)
     for b0 in (0, 128, 248):
         assert torch.equal(small.run(x[b0:b0 + 8]), y[b0:b0 + 8]), b0
+
+
+def test_evaluate_entry_point_with_kernels(cuda_device, tmp_path):
+    """`-e --use-kernel True` on two batches of MNIST-shaped and one of CIFAR-shaped stand-in data:
+    the converted model runs on the CUDA kernels, and agrees with its own fp32 path on nearly every
+    prediction (they differ only by the fixed-point rounding of the activations)."""
+    from deepshift_b200 import evaluate
+    common = ['-s', '100', '-st', 'PS', '-wb', '5', '-ab', '4', '12', '-e', '--out-dir', str(tmp_path)]
+    for ds, extra in (('mnist', ['--type', 'conv', '-b', '32', '--synthetic-images', '64']),
+                      ('cifar10', ['-a', 'resnet20', '-b', '16', '--synthetic-images', '16'])):
+        rows = {}
+        for uk in ('True', 'False'):
+            lines = []
+            rows[uk] = evaluate.main(['--dataset', ds] + extra + common + ['--use-kernel', uk, '--desc', uk],
+                                     out=lines.append)
+            assert any("dataset unavailable on this box" in l for l in lines)
+        assert np.isfinite(rows['True'][0]) and abs(rows['True'][0] - rows['False'][0]) < 0.05 * max(1.0, rows['False'][0])

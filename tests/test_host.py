@@ -275,3 +275,94 @@ def test_argument_checks_need_no_gpu():
     assert lib.ds_version() >= 100
     with pytest.raises(RuntimeError, match="bad argument"):
         _ffi.check(1, "probe")
+
+
+# --------------------------------------------------------------------------- evaluation entry point
+def test_evaluate_flags_follow_the_reference_drivers():
+    from deepshift_b200 import evaluate
+    a = evaluate.build_parser().parse_args(
+        ['--dataset', 'imagenet', '-a', 'resnet18', '-s', '1000', '-st', 'PS', '-wb', '5', '-ab', '4', '12',
+         '--use-kernel', 'True', '-e', '-b', '64', '/nonexistent'])
+    assert (a.arch, a.shift_depth, a.shift_type, a.weight_bits, a.batch_size) == ('resnet18', 1000, 'PS', 5, 64)
+    assert a.use_kernel is True and a.evaluate is True and [int(v) for v in a.activation_bits] == [4, 12]
+    assert a.data == '/nonexistent'
+    with pytest.raises(SystemExit):
+        evaluate.main(['--dataset', 'mnist', '--type', 'linear'])            # no -e: inference only
+    with pytest.raises(SystemExit):
+        evaluate.main(['--dataset', 'mnist', '-e', '-ab', '4'])              # needs two values
+
+
+def test_evaluate_runs_on_synthetic_data_and_writes_the_csv(tmp_path):
+    """No dataset on the box: the seeded stand-in is announced, the whole user path runs (model, conversion
+    to DeepShift-PS, validation loop, meters) on the fp32 path, and test_log.csv has the reference's columns."""
+    import csv
+    from deepshift_b200 import evaluate, modules
+    lines = []
+    row = evaluate.main(['--dataset', 'mnist', '--type', 'conv', '-s', '10', '-st', 'PS', '-ab', '4', '12', '-e',
+                         '-b', '16', '--synthetic-images', '40', '--out-dir', str(tmp_path), '--desc', 't'],
+                        out=lines.append)
+    assert any("dataset unavailable on this box" in l for l in lines)
+    assert any("4 layer(s) converted" in l for l in lines)
+    loss, top1, top5, bt = row
+    assert np.isfinite(loss) and 0.0 <= top1 <= top5 <= 100.0 and bt > 0
+    path = tmp_path / 'mnist' / 'mnist_conv' / 'shift_10_PS_wb5_ab4.12_t' / 'test_log.csv'
+    rows = list(csv.reader(open(path)))
+    assert rows[0] == ['test_loss', 'test_top1_acc', 'test_top5_acc', 'test_time', 'cumulative_time']
+    assert len(rows) == 2 and len(rows[1]) == 5
+    assert evaluate.topk_correct(torch.tensor([[0.1, 0.9, 0.0], [0.5, 0.2, 0.3]]), torch.tensor([1, 2]), ks=(1, 2)) == [1, 2]
+    m, _ = evaluate.build_model(evaluate.build_parser().parse_args(['--dataset', 'cifar10', '-a', 'resnet20', '-e']))
+    assert sum(1 for x in m.modules() if isinstance(x, torch.nn.Conv2d)) == 19
+    assert tuple(m(torch.zeros(2, 3, 32, 32)).shape) == (2, 10)
+
+
+# --------------------------------------------------------------------------- the binding inside the reference tree
+def test_reference_tree_calls_the_stub_with_the_right_arguments(monkeypatch):
+    """The reference's own Python dispatcher (deepshift/kernels/kernels.py:10-74), imported from the
+    reference checkout, driven over deepshift_b200/reference_binding/deepshift_cuda.py: a recording
+    stand-in for the C library shows that every call reaches the C ABI with the argument list
+    include/deepshift_b200.h declares.  (No GPU here: the same stub against the real library is a
+    GPU test.)  Skipped where the reference checkout is not mounted."""
+    import importlib
+    import sys
+    import types
+    root = os.environ.get("DEEPSHIFT_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.isdir(os.path.join(root, "pytorch", "deepshift")):
+        pytest.skip("reference checkout not mounted")
+    binding = os.path.join(ROOT, "deepshift_b200", "reference_binding")
+    monkeypatch.syspath_prepend(os.path.join(root, "pytorch"))
+    monkeypatch.syspath_prepend(binding)
+    for name in [n for n in sys.modules if n == "deepshift" or n.startswith("deepshift.") or n in ("deepshift_cuda", "deepshift_cpu")]:
+        monkeypatch.delitem(sys.modules, name)
+    monkeypatch.setitem(sys.modules, "deepshift_cpu", types.ModuleType("deepshift_cpu"))
+    stub = importlib.import_module("deepshift_cuda")
+    assert os.path.dirname(stub.__file__) == binding
+    calls = []
+
+    class FakeLib:
+        def __getattr__(self, name):
+            def fn(*args):
+                calls.append((name, args))
+                return 0
+            return fn
+    monkeypatch.setattr(stub, "_lib", FakeLib())
+    ref_kernels = importlib.import_module("deepshift.kernels.kernels")
+    ref_utils = importlib.import_module("deepshift.utils")
+    assert ref_kernels.deepshift_cuda is stub
+    x = torch.zeros((3, 20), dtype=torch.int32)
+    shift, bias = torch.zeros((7, 20)), torch.zeros(7, dtype=torch.int32)
+    cw = ref_utils.ConcWeight(torch.zeros((7, 5), dtype=torch.int32), base=0, bits=6)
+    out = ref_kernels.linear(x, shift, None, bias, cw, use_cuda=True)
+    name, a = calls[-1]
+    assert name == "ds_linear_i32" and tuple(out.shape) == (3, 7)
+    assert a[:4] == (x.data_ptr(), cw.data.data_ptr(), bias.data_ptr(), out.data_ptr())
+    assert a[4:] == (3, 20, 7, 6, 0, 0, None)          # M, K, N, bits, base, act_bits, stream
+    xi = torch.zeros((2, 3, 8, 8), dtype=torch.int32)
+    shift = torch.zeros((5, 3, 3, 3))
+    cw = ref_utils.ConcWeight(torch.zeros((5, 7), dtype=torch.int32), base=0, bits=6)
+    bias = torch.zeros(5, dtype=torch.int32)
+    out = ref_kernels.conv2d(xi, shift, None, bias, cw, stride=(2, 2), padding=(1, 1), use_cuda=True)
+    name, a = calls[-1]
+    assert name == "ds_conv2d_i32" and tuple(out.shape) == (2, 5, 4, 4)
+    # B, C, H, W of the tensor kernels.py has already padded; OC; window; strides; no padding; bits, base, act_bits
+    assert a[4:] == (2, 3, 10, 10, 5, 3, 3, 2, 2, 0, 0, 6, 0, 0, None)
+    assert a[1:4] == (cw.data.data_ptr(), bias.data_ptr(), out.data_ptr())
