@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     const int t = threadIdx.x;
     const int m0 = blockIdx.x * BM;
     const int n0 = blockIdx.y * BN;
+    if (p.gate && *p.gate != p.gate_want) return;  // the other arithmetic path serves this input
     // A warp covers 8 x 4 thread tiles: 8 along the direction in which the output is contiguous
     // (m for the NCHW convolution output, n for the [M,N] linear output), so that both operand
     // fragments come from few shared-memory wavefronts and stores fill whole sectors.
@@ -470,7 +471,7 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     p.splits = 1;
     p.tiles_per_split = p.ntiles;
     const bool plain = p.out_kind == DS_OUT_I32 && !p.relu && !p.requant && !p.round_f32 && !p.residual && !p.operand_out;
-    if (MODE == MODE_INT && AM == AM_LINEAR && plain && gx * gy < 148) {
+    if (MODE == MODE_INT && AM == AM_LINEAR && plain && !p.gate && gx * gy < 148) {
         // Few output tiles (small batch): split K across gridDim.z until two CTAs per SM have work;
         // the partial sums meet through integer atomics in the zeroed output.
         int splits = 1;
@@ -592,6 +593,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.partial_bytes = f.workspace_bytes - (long long)kWorkspaceCounters * 4;
         p.counter_slots = kWorkspaceCounters;
     }
+    if (p.counter_slots > kWorkspaceGateSlot) p.counter_slots = kWorkspaceGateSlot;  // the last word is the range flag
     p.wd = nullptr;
     p.negpre = nullptr;
     p.npad = 0;
@@ -631,7 +633,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.in_add2 = int(2u * unsigned(p.rq_add) + unsigned(kHalfMagicBits + 1));
     // FP32-pipe path: needs base == 0, every |x| <= 2^(act_bits-1) <= 2^17, and room for at
     // least one k-tile of terms (each of magnitude <= 2^(act_bits-1) + 1) between drains.
-    int ab = f.act_bits;
+    int ab = f.act_bits == DS_ACT_BITS_AUTO ? 0 : f.act_bits;
     if (f.in_kind == DS_IN_F32_CONV || in_clamp || in_operand) ab = sign_mode ? F + 2 : I + F;
     if (f.in_kind == DS_IN_F32_LINEAR) ab = 0;
     use_fp = (base == 0 && ab >= 1 && ab <= 18);
@@ -644,6 +646,43 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     }
     if (in_operand && !use_fp) return DS_ERR_UNSUPPORTED;  // the operand form exists for the FP32-pipe path only
     return DS_OK;
+}
+
+// Sets *flag to 1 if any |x| exceeds `limit` (the flag was zeroed before).  One pass, 16-byte loads
+// for the aligned bulk.
+__global__ void __launch_bounds__(256) range_kernel(const int* __restrict__ x, long long n, int limit, int* flag)
+{
+    bool over = false;
+    const long long n4 = ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) ? n / 4 : 0;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const int4 v = __ldg(reinterpret_cast<const int4*>(x) + i);
+        over |= (v.x > limit) | (v.x < -limit) | (v.y > limit) | (v.y < -limit) | (v.z > limit) | (v.z < -limit) |
+                (v.w > limit) | (v.w < -limit);
+    }
+    for (long long i = 4 * n4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int v = __ldg(x + i);
+        over |= (v > limit) | (v < -limit);
+    }
+    if (over) *flag = 1;
+}
+
+// act_bits = DS_ACT_BITS_AUTO: can this call be served by the two gated launches?  It needs int32
+// input without a promise, right shifts only and a workspace (whose last counter word is the flag).
+bool auto_range(const ds_fuse_t* fuse, int base)
+{
+    return fuse && fuse->act_bits == DS_ACT_BITS_AUTO && fuse->in_kind == DS_IN_I32 && base == 0 && fuse->workspace &&
+           fuse->workspace_bytes >= (long long)kWorkspaceCounters * 4;
+}
+
+// Zeroes the flag and measures the range of x on `st`; returns the flag's device address.
+int* launch_range(const void* x, long long n, const ds_fuse_t* fuse, cudaStream_t st)
+{
+    int* flag = static_cast<int*>(fuse->workspace) + kWorkspaceGateSlot;
+    if (cudaMemsetAsync(flag, 0, sizeof(int), st) != cudaSuccess) return nullptr;
+    const long long want = (n / 4 + 255) / 256 + 1;
+    range_kernel<<<unsigned(want > 148 * 16 ? 148 * 16 : want), 256, 0, st>>>(static_cast<const int*>(x), n, 1 << 15, flag);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? flag : nullptr;
 }
 
 int check_ptrs(const void* x, const void* packed, const void* out)
@@ -667,6 +706,30 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     if (M == 0) return DS_OK;
     int rc = check_ptrs(x, packed, out);
     if (rc) return rc;
+    if (auto_range(fuse, base) && M > 64) {
+        // measure the range once, then launch both arithmetic paths gated on the result
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        int* flag = launch_range(x, (long long)M * K, fuse, st);
+        if (!flag) return DS_ERR_CUDA;
+        ds_fuse_t f = *fuse;
+        for (int pass = 0; pass < 2; ++pass) {
+            f.act_bits = pass == 0 ? 16 : 0;
+            GemmParams g = {};
+            g.x = x; g.packed = packed; g.bias = bias; g.out = out;
+            g.M = M; g.K = K; g.N = N;
+            bool gfp = false;
+            rc = setup_common(g, bits, base, &f, gfp);
+            if (rc) return rc;
+            if (g.residual && (reinterpret_cast<uintptr_t>(g.residual) & 3u)) return DS_ERR_ALIGN;
+            g.prepared = nullptr;
+            g.prepared_bytes = 0;
+            g.gate = flag;
+            g.gate_want = pass;
+            rc = launch_am<AM_LINEAR>(g, gfp, st);
+            if (rc) return rc;
+        }
+        return DS_OK;
+    }
     GemmParams p = {};
     p.x = x; p.packed = packed; p.bias = bias; p.out = out;
     p.M = M; p.K = K; p.N = N;
@@ -723,6 +786,27 @@ int conv2d_run(const void* x, const int32_t* packed, const int32_t* bias, void* 
     p.magic_khw = magic_of(KH * KW);
     p.magic_kw = magic_of(KW);
     p.magic_kh = magic_of(KH);
+    if (!prepare && auto_range(fuse, base)) {
+        // measure the range once, then launch both arithmetic paths gated on the result
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        int* flag = launch_range(x, (long long)B * C * H * W, fuse, st);
+        if (!flag) return DS_ERR_CUDA;
+        ds_fuse_t f = *fuse;
+        for (int pass = 0; pass < 2; ++pass) {
+            f.act_bits = pass == 0 ? 16 : 0;
+            f.prepared = nullptr;   // expanded ahead of time for one path only: not used here
+            f.prepared_bytes = 0;
+            GemmParams g = p;
+            bool gfp = false;
+            const int rc = setup_common(g, bits, base, &f, gfp);
+            if (rc) return rc;
+            g.gate = flag;
+            g.gate_want = pass;
+            const int rl = launch_conv(g, gfp, st);
+            if (rl) return rl;
+        }
+        return DS_OK;
+    }
     bool fp = false;
     const int rc = setup_common(p, bits, base, fuse, fp);
     if (rc) return rc;

@@ -63,6 +63,11 @@ struct GemmParams {
     const int* negpre;   // [ntiles + 1][npad]: negative weights of a column in the k-tiles before t
     int npad;            // grid_n * BN
     int* err_flag;       // set to 1 by a kernel whose bounded wait ran out
+    // Range-gated launch (act_bits = DS_ACT_BITS_AUTO): the kernel runs only if *gate == gate_want.  A
+    // one-pass kernel has written 0 there when every activation is within the FP32-pipe bound, else 1;
+    // the FP32-pipe launch wants 0, the integer-path launch behind it wants 1.  Null = always run.
+    const int* gate;
+    int gate_want;
     // weights expanded ahead of time by the caller (ds_conv2d_prepare)
     const void* prepared;
     long long prepared_bytes;
@@ -81,6 +86,8 @@ struct GemmParams {
 
 // Leading int32 slots of a caller's workspace that hold arrival counters; partial sums follow.
 constexpr int kWorkspaceCounters = 16384;
+// The last counter word is never handed out as a counter: it holds the range flag of gated launches.
+constexpr int kWorkspaceGateSlot = kWorkspaceCounters - 1;
 
 struct alignas(16) KEntry {
     int off;  // byte offset of the tap (table mode) or of the row start (row mode)

@@ -179,6 +179,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 
     const int t = threadIdx.x;
     const int total_items = p.full_units + p.tail_items * p.tail_splits;
+    if (p.gate && *p.gate != p.gate_want) return;  // the other arithmetic path serves this input
 
     // ---- set-up by all threads ------------------------------------------------------------------
     for (int f = t; f < (1 << p.dec.fw); f += WS_NT) {
@@ -1018,8 +1019,9 @@ int ws_launch_cfg(GemmParams p, cudaStream_t st)
             p.tail_tps = (p.ntiles + p.tail_splits - 1) / p.tail_splits;
             p.tail_splits = (p.ntiles + p.tail_tps - 1) / p.tail_tps;
         }
-    } else if (p.counters && !p.partials && tiles <= p.counter_slots && p.ntiles >= 16 &&
+    } else if (p.counters && !p.partials && tiles <= p.counter_slots && p.ntiles >= 16 && !p.gate &&
                static_cast<const void*>(p.residual) != p.out) {
+        // (not for a gated launch either: zeroing the output would undo the other path's result)
         // (an in-place residual add, residual == out, would be wiped by the zeroing below)
         // Split-K of every tile through integer atomics on the zeroed output, for callers whose
         // workspace holds counters only: used when the tiles alone fill the SMs badly.

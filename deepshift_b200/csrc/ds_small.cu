@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
     __shared__ int2 lut[256];                       // (right shift, multiplier) per field value
     __shared__ int part[SM_WARPS][MR * CN];         // partial sums of the warps that share a column group
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    if (p.gate && *p.gate != p.gate_want) return;
     for (int f = t; f < (1 << p.dec.fw); f += SM_THREADS) {
         int shv, mul;
         decode_int(uint32_t(f), p.dec, true, shv, mul);

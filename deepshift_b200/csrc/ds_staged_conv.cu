@@ -600,7 +600,7 @@ int st_launch(const CUtensorMap& map, StagedConvParams p, void* workspace, long 
         int splits = 1;
         for (int sp = 2; sp <= 4; ++sp) {
             if (p.ntiles / sp < 4) break;
-            if ((long long)tail * sp * SLOT_BYTES > partial_bytes || tail > kWorkspaceCounters) break;
+            if ((long long)tail * sp * SLOT_BYTES > partial_bytes || tail > kWorkspaceGateSlot) break;
             const long long rounds = ((long long)tail * sp + sms - 1) / sms;
             const double cost = double(rounds) / sp + 0.04;
             if (cost < best - 0.05) {

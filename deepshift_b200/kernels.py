@@ -105,8 +105,15 @@ def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=F
     return f
 
 
-def linear(input, shift, sign, bias=None, conc_weight=None, use_cuda=True, act_bits=0):
-    """int32 [M,K] -> int32 [M,N].  ``shift``/``sign`` only give N (as in kernels.py:14)."""
+ACT_BITS_AUTO = -1   # DS_ACT_BITS_AUTO: the library measures the range of the activations on the device
+
+
+def linear(input, shift, sign, bias=None, conc_weight=None, use_cuda=True, act_bits=None):
+    """int32 [M,K] -> int32 [M,N].  ``shift``/``sign`` only give N (as in kernels.py:14).
+
+    ``act_bits`` (not in the reference): a promise that every |x| <= 2^(act_bits-1), which selects the
+    FP32-pipe path (1..18); 0 = the exact integer path; None (default) = let the library look at the
+    data and take the FP32-pipe path when it can (see DS_ACT_BITS_AUTO).  Results are identical."""
     if not use_cuda:
         _no_cpu()
     assert conc_weight is not None
@@ -118,7 +125,8 @@ def linear(input, shift, sign, bias=None, conc_weight=None, use_cuda=True, act_b
     N = shift.size(0)
     out = torch.empty([M, N], dtype=torch.int32, device=input.device)
     # ds_linear_i32 plus the workspace (expanded weights, shared tiles when few tiles fill the SMs)
-    f = _fuse(act_bits=act_bits, workspace=workspace(input.device) if M > 64 else None)
+    f = _fuse(act_bits=ACT_BITS_AUTO if act_bits is None else act_bits,
+              workspace=workspace(input.device) if M > 64 else None)
     with torch.cuda.device(input.device):
         rc = _ffi.lib().ds_linear_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),
@@ -140,8 +148,8 @@ def _conv_geometry(input, shift, stride, padding, dilation, groups):
 
 
 def conv2d(input, shift, sign, bias=None, conc_weight=None, stride=1, padding=0, dilation=1, groups=1,
-           use_cuda=True, act_bits=0):
-    """int32 NCHW (unpadded) -> int32 NCHW."""
+           use_cuda=True, act_bits=None):
+    """int32 NCHW (unpadded) -> int32 NCHW.  ``act_bits``: see ``linear``."""
     if not use_cuda:
         _no_cpu()
     assert conc_weight is not None
@@ -152,7 +160,7 @@ def conv2d(input, shift, sign, bias=None, conc_weight=None, stride=1, padding=0,
     B, C, H, W, OC, KH, KW, sh, sw, ph, pw, OH, OW = _conv_geometry(input, shift, stride, padding, dilation, groups)
     out = torch.empty([B, OC, OH, OW], dtype=torch.int32, device=input.device)
     # ds_conv2d_i32 plus the split-K counter workspace (layers with few output tiles)
-    f = _fuse(act_bits=act_bits, workspace=workspace(input.device))
+    f = _fuse(act_bits=ACT_BITS_AUTO if act_bits is None else act_bits, workspace=workspace(input.device))
     with torch.cuda.device(input.device):
         rc = _ffi.lib().ds_conv2d_ex(input.data_ptr(), conc_weight.data.data_ptr(),
                                      bias.data_ptr() if bias is not None else None, out.data_ptr(),

@@ -7,8 +7,10 @@ this module, and its ``linear`` / ``conv2d`` / ``compress_sign_and_shift`` (kern
 the three functions below with torch CUDA tensors exactly as they call the pybind ones.
 
 ``act_bits`` is passed as 0 (no promise about the activations' range), which selects the exact
-integer path for any int32 input.  ``kernels.py:32-36`` hands over an already padded tensor, so the
-convolution is asked for no padding of its own.
+integer path for any int32 input; the fused entry points (``ds_conv2d_ex`` with a workspace and
+``DS_ACT_BITS_AUTO``) can pick the faster FP32-pipe path by looking at the data.
+``kernels.py:32-36`` hands over an already padded tensor, so the convolution is asked for no
+padding of its own.
 """
 import ctypes
 import os

@@ -42,6 +42,14 @@ typedef enum {
     DS_ERR_SCRATCH = 6       /* ds_conv2d_noalloc: more output tiles than its fixed scratch holds */
 } ds_status;
 
+/* ds_fuse_t.act_bits: no promise about the range of int32 inputs, but let the library find out.  A
+ * one-pass kernel looks for an |x| beyond 2^15; the FP32-pipe launch and the integer-path launch are
+ * both enqueued, each gated on what it found (one of them returns at once).  About twice as fast as
+ * act_bits = 0 for activations that a 16-bit quantiser produced, exact for all others.  Needs
+ * fuse->workspace (its last counter word holds the result); without one, with base < 0 or for other
+ * input kinds it means the same as 0. */
+#define DS_ACT_BITS_AUTO (-1)
+
 /* Input element kinds of the *_ex entry points. */
 enum {
     DS_IN_I32 = 0,       /* int32 fixed point (what the reference kernels receive)                         */
@@ -93,7 +101,8 @@ typedef struct {
     int reserved[3];
     void *workspace;        /* optional scratch for sharing an output tile (256 rows x 128 or 64
                                columns) between CTAs along K.  The first 16384 int32 are arrival
-                               counters: zero them once; every launch leaves them zero.  Bytes beyond
+                               counters: zero them once; every launch leaves them zero (the last of
+                               them is the range flag of DS_ACT_BITS_AUTO, rewritten by each such call).  Bytes beyond
                                those 64 KiB (any contents) hold, per launch, the layer's weights
                                expanded to fp32 (4 bytes per weight, when the launch has at least 8
                                row tiles) and partial sums, 128 KiB per shared tile and split; about

@@ -105,7 +105,7 @@ def test_linear_on_warp_specialised_kernel(oracle, cuda_device, M, K, N):
     for _ in range(2):  # the second launch finds the arrival counters as the first left them
         out = kernels.linear(xt, _t(shift, cuda_device), None, bt, cw, act_bits=16)
         assert np.array_equal(out.cpu().numpy(), ref)
-    assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
+    assert int(kernels.workspace(cuda_device)[:16383].abs().sum()) == 0
     # the same layer without a workspace (plain C entry point) and on the exact integer path
     for act_bits in (16, 0):
         out2 = torch.empty_like(out)
@@ -497,7 +497,7 @@ def test_conv_split_k_with_workspace(oracle, cuda_device, out_f32):
                                    act_integer_bits=I, act_fraction_bits=F, relu=True, residual=_t(res, cuda_device),
                                    round_f32=True)
         assert np.array_equal(out.cpu().numpy(), want)
-    assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
+    assert int(kernels.workspace(cuda_device)[:16383].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("B", [49, 68])
@@ -516,7 +516,7 @@ def test_conv_tail_wave_is_split(oracle, cuda_device, B):
         out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device),
                              _cw(shift, sign, cuda_device), 1, 1, act_bits=16)
         assert np.array_equal(out.cpu().numpy(), ref)
-    assert int(kernels.workspace(cuda_device)[:16384].abs().sum()) == 0
+    assert int(kernels.workspace(cuda_device)[:16383].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("shape", [(12, 16, 28, 28, 40, 3, 1, 1),    # four-pixel staging, 37 row tiles
@@ -934,3 +934,28 @@ def test_reference_binding_stub_against_the_library(oracle, cuda_device):
     zero_bias = torch.zeros([N], dtype=torch.int32, device=cuda_device)
     stub.DEEP_SHIFT_LINEAR(_t(xl, cuda_device), cw.data, zero_bias, outl, cw.base, cw.bits, N)
     assert np.array_equal(outl.cpu().numpy(), oracle.linear(xl, sl, gl, None))
+
+
+def test_act_bits_auto_picks_the_path_by_looking_at_the_data(oracle, cuda_device):
+    """The reference signature makes no promise about the activations' range.  By default the
+    library measures it on the device and enqueues both arithmetic paths, each gated on the result:
+    16-bit activations run on the FP32 pipe, wider ones on the integer pipe, both exact."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(2718)
+    B, C, H, OC = 6, 16, 28, 40
+    shift, sign = weights(rng, (OC, C, 3, 3))
+    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
+    cw = _cw(shift, sign, cuda_device)
+    for x, flag in ((acts_q16(rng, (B, C, H, H)), 0), (acts_wide(rng, (B, C, H, H), 24), 1)):
+        ref = oracle.conv2d(x, shift, sign, bias, (1, 1), (1, 1))
+        out = kernels.conv2d(_t(x, cuda_device), _t(shift, cuda_device), None, _t(bias, cuda_device), cw, 1, 1)
+        assert np.array_equal(out.cpu().numpy(), ref)
+        assert int(kernels.workspace(cuda_device)[16383]) == flag
+    M, K, N = 300, 512, 200
+    sl, gl = weights(rng, (N, K))
+    cwl = _cw(sl, gl, cuda_device)
+    for x, flag in ((acts_q16(rng, (M, K)), 0), (acts_wide(rng, (M, K), 24), 1)):
+        out = kernels.linear(_t(x, cuda_device), _t(sl, cuda_device), None, None, cwl)
+        assert np.array_equal(out.cpu().numpy(), oracle.linear(x, sl, gl, None))
+        assert int(kernels.workspace(cuda_device)[16383]) == flag
+    assert int(kernels.workspace(cuda_device)[:16383].abs().sum()) == 0
