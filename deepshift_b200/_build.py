@@ -16,6 +16,11 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libdeepshift_b200.so")
 STAMP = os.path.join(LIB_DIR, "sources.sha256")
+# The checked flavour: every global access of the linear / convolution kernels tests its address
+# first (see "Checked build" in include/deepshift_b200.h).  Slower; for tests and for debugging.
+CHECKED_LIB_PATH = os.path.join(LIB_DIR, "libdeepshift_b200_checked.so")
+CHECKED_STAMP = os.path.join(LIB_DIR, "sources_checked.sha256")
+CHECKED_FLAGS = ("-DDS_BOUNDS_CHECK",)
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -39,10 +44,11 @@ def _digest():
     return h.hexdigest()
 
 
-def is_current():
+def is_current(checked=False):
+    lib, stamp = (CHECKED_LIB_PATH, CHECKED_STAMP) if checked else (LIB_PATH, STAMP)
     try:
-        with open(STAMP) as fh:
-            return os.path.exists(LIB_PATH) and fh.read().strip() == _digest()
+        with open(stamp) as fh:
+            return os.path.exists(lib) and fh.read().strip() == _digest()
     except OSError:
         return False
 
@@ -52,18 +58,22 @@ def nvcc_path():
     return cand if os.path.exists(cand) else None
 
 
-def build(force=False, verbose=False, extra_flags=()):
+def build(force=False, verbose=False, extra_flags=(), checked=False):
     """Compile the library if the sources changed.  Returns the library path.
 
     Every ``.cu`` file is compiled to an object file by its own nvcc process (they run side by
-    side), then the objects are linked into the shared library."""
-    if not force and is_current():
-        return LIB_PATH
+    side), then the objects are linked into the shared library.  ``checked=True`` builds the
+    bounds-checking flavour beside the normal one."""
+    lib_path, stamp = (CHECKED_LIB_PATH, CHECKED_STAMP) if checked else (LIB_PATH, STAMP)
+    if checked:
+        extra_flags = tuple(extra_flags) + CHECKED_FLAGS
+    if not force and is_current(checked):
+        return lib_path
     nvcc = nvcc_path()
     if nvcc is None:
-        raise RuntimeError("nvcc not found and %s is missing or stale" % LIB_PATH)
+        raise RuntimeError("nvcc not found and %s is missing or stale" % lib_path)
     os.makedirs(LIB_DIR, exist_ok=True)
-    obj_dir = os.path.join(LIB_DIR, "obj")
+    obj_dir = os.path.join(LIB_DIR, "obj_checked" if checked else "obj")
     os.makedirs(obj_dir, exist_ok=True)
     env = dict(os.environ)
     env.pop("CC", None)
@@ -86,16 +96,17 @@ def build(force=False, verbose=False, extra_flags=()):
     bad = [obj for obj, rc, _ in results if rc]
     if bad:
         raise RuntimeError("nvcc failed for: " + ", ".join(os.path.basename(b) for b in bad))
-    cmd = [nvcc, "-shared", "-ccbin", "g++", "-o", LIB_PATH] + [obj for obj, _, _ in results]
+    cmd = [nvcc, "-shared", "-ccbin", "g++", "-o", lib_path] + [obj for obj, _, _ in results]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True, env=env)
     shutil.rmtree(obj_dir, ignore_errors=True)
-    with open(STAMP, "w") as fh:
+    with open(stamp, "w") as fh:
         fh.write(_digest())
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
     import sys
-    print(build(force=True, verbose=True, extra_flags=sys.argv[1:]))
+    flags = [a for a in sys.argv[1:] if a != "--checked"]
+    print(build(force=True, verbose=True, extra_flags=flags, checked="--checked" in sys.argv))

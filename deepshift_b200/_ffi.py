@@ -62,6 +62,10 @@ _SIGNATURES = {
     "ds_avgpool_fix_i32": [_VP, _VP, _I, _I, _I, _I, _I, _VP],
     "ds_pipe_peak": [_I, _I, ctypes.POINTER(ctypes.c_double), _VP],
     "ds_last_kernel_error": [ctypes.POINTER(ctypes.c_int)],
+    "ds_bounds_status": [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)],
+    "ds_bounds_debug_shrink_x": [_LL],
+    "ds_unopt_linear_f32": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP],
+    "ds_unopt_conv2d_f32": [_VP, _VP, _VP, _VP] + [_I] * 11 + [_VP],
     "ds_staged_fill": [ctypes.POINTER(Staged), _VP],
     "ds_stage_nchw": [_VP, _I, _I, _I, ctypes.POINTER(Staged), _VP],
     "ds_staged_prepare": [_VP, _I, _I, _I, _I, _I, _I, _VP, _LL, ctypes.POINTER(ctypes.c_longlong), _VP],
@@ -75,13 +79,16 @@ def lib():
     """Loads (building first if the sources changed and nvcc is present) the CUDA library."""
     global _lib
     if _lib is None:
-        if not _build.is_current() and _build.nvcc_path() is not None:
-            _build.build()
-        if not os.path.exists(_build.LIB_PATH):
+        # DEEPSHIFT_B200_CHECKED=1 selects the bounds-checking flavour of the library
+        checked = os.environ.get("DEEPSHIFT_B200_CHECKED", "") not in ("", "0")
+        path = _build.CHECKED_LIB_PATH if checked else _build.LIB_PATH
+        if not _build.is_current(checked) and _build.nvcc_path() is not None:
+            _build.build(checked=checked)
+        if not os.path.exists(path):
             raise RuntimeError(
                 "deepshift_b200: CUDA library %s is missing and cannot be built (no nvcc); "
-                "there is no CPU fallback" % _build.LIB_PATH)
-        l = ctypes.CDLL(_build.LIB_PATH)
+                "there is no CPU fallback" % path)
+        l = ctypes.CDLL(path)
         for name, args in _SIGNATURES.items():
             fn = getattr(l, name)
             fn.argtypes = args

@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 #pragma unroll
                 for (int kw = 0; kw < KW; ++kw) {
                     int v = padv;
-                    if (rv && (colmask & (1u << kw))) v = __ldg(rowp + kw);
+                    if (rv && (colmask & (1u << kw)) && DS_X_OK(p, rowp + kw, 4)) v = __ldg(rowp + kw);
                     a_reg[u * KW + kw] = v;
                 }
             }
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
                 int v = padv;
                 if (kl < BKT) {
                     const int4 ke = *reinterpret_cast<const int4*>(&s.ktab[buf][kl]);
-                    if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u)
+                    if (((rowmask >> ke.y) & (colmask >> ke.z) & 1u) != 0u && DS_X_OK(p, x_pix + ke.x, 4))
                         v = __ldg(reinterpret_cast<const int*>(x_pix + ke.x));
                 }
                 a_reg[e] = v;
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 #pragma unroll
             for (int e = 0; e < A_ELEMS; ++e) {
                 int v = padv;
-                if (((rowmask >> e) & 1u) && !ktail) v = __ldg(src + (long long)e * A_MSTEP * p.K);
+                if (((rowmask >> e) & 1u) && !ktail && DS_X_OK(p, src + (long long)e * A_MSTEP * p.K, 4)) v = __ldg(src + (long long)e * A_MSTEP * p.K);
                 a_reg[e] = v;
             }
         }
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
 #pragma unroll
         for (int e = 0; e < EW; ++e) {
             uint32_t w = 0;
-            if (w_ptr[e] && w0 + w_jw[e] < p.dec.row_len) w = uint32_t(__ldg(w_ptr[e] + w0));
+            if (w_ptr[e] && w0 + w_jw[e] < p.dec.row_len && DS_W_OK(p, w_ptr[e] + w0, 4)) w = uint32_t(__ldg(w_ptr[e] + w0));
             w_reg[e] = w;
         }
     };
@@ -685,6 +685,17 @@ int* launch_range(const void* x, long long n, const ds_fuse_t* fuse, cudaStream_
     return cudaGetLastError() == cudaSuccess ? flag : nullptr;
 }
 
+// Checked build: the extents the kernels test their addresses against.
+long long g_check_shrink_x = 0;  // ds_bounds_debug_shrink_x: bytes taken off the declared extent of x
+
+void set_check_extents(GemmParams& p, long long x_elems)
+{
+    p.chk_x_bytes = x_elems * 4 - g_check_shrink_x;
+    p.chk_w_bytes = (long long)p.N * p.dec.row_len * 4;
+    p.chk_o_bytes = (long long)p.M * p.N * 4;
+    p.chk_status = bounds_status_ptr();
+}
+
 int check_ptrs(const void* x, const void* packed, const void* out)
 {
     if (!x || !packed || !out) return DS_ERR_BAD_ARG;
@@ -725,6 +736,7 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
             g.prepared_bytes = 0;
             g.gate = flag;
             g.gate_want = pass;
+            set_check_extents(g, (long long)M * K);
             rc = launch_am<AM_LINEAR>(g, gfp, st);
             if (rc) return rc;
         }
@@ -739,6 +751,7 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     if (p.residual && (reinterpret_cast<uintptr_t>(p.residual) & 3u)) return DS_ERR_ALIGN;
     p.prepared = nullptr;  // weights expanded ahead of time exist for convolutions only
     p.prepared_bytes = 0;
+    set_check_extents(p, (long long)M * K);
     // Small batches run on the integer pipe: up to 16 rows on the kernel that splits K across the
     // lanes of a warp, up to 64 rows on the block kernel with a 64-row tile (K split across CTAs
     // when nothing is fused into the epilogue).
@@ -802,6 +815,7 @@ int conv2d_run(const void* x, const int32_t* packed, const int32_t* bias, void* 
             if (rc) return rc;
             g.gate = flag;
             g.gate_want = pass;
+            set_check_extents(g, (long long)B * C * H * W);
             const int rl = launch_conv(g, gfp, st);
             if (rl) return rl;
         }
@@ -812,6 +826,7 @@ int conv2d_run(const void* x, const int32_t* packed, const int32_t* bias, void* 
     if (rc) return rc;
     p.prepare_only = prepare ? 1 : 0;
     p.needed_out = needed_out;
+    set_check_extents(p, (long long)B * C * H * W);
     return launch_conv(p, fp, static_cast<cudaStream_t>(stream));
 }
 
@@ -901,4 +916,19 @@ extern "C" int ds_conv2d_noalloc(const void* x, const int32_t* packed, const int
     f.workspace = counters;
     f.workspace_bytes = (long long)kNoAllocMaxTiles * (long long)sizeof(int);
     return ds_conv2d_ex(x, packed, bias, out, B, C, H, W, OC, KH, KW, sh, sw, ph, pw, bits, base, &f, stream);
+}
+
+// Checked build only: declares the activations `bytes` shorter than they are for the calls that
+// follow (0 restores the truth), so that a test can watch the checks catch loads beyond the declared
+// end without any access leaving the real buffer.  DS_ERR_UNSUPPORTED in a normal build.
+extern "C" int ds_bounds_debug_shrink_x(long long bytes)
+{
+#ifdef DS_BOUNDS_CHECK
+    if (bytes < 0) return DS_ERR_BAD_ARG;
+    ds::g_check_shrink_x = bytes;
+    return DS_OK;
+#else
+    (void)bytes;
+    return DS_ERR_UNSUPPORTED;
+#endif
 }

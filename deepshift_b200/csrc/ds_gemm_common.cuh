@@ -68,6 +68,10 @@ struct GemmParams {
     // the FP32-pipe launch wants 0, the integer-path launch behind it wants 1.  Null = always run.
     const int* gate;
     int gate_want;
+    // Checked build (-DDS_BOUNDS_CHECK) only: byte extents of x, of the packed weights and of the output
+    // (residual and operand_out have the output's element count), and where the first violation goes.
+    long long chk_x_bytes, chk_w_bytes, chk_o_bytes;
+    int* chk_status;
     // weights expanded ahead of time by the caller (ds_conv2d_prepare)
     const void* prepared;
     long long prepared_bytes;
@@ -95,6 +99,31 @@ struct alignas(16) KEntry {
     int kw;
     int pad;
 };
+
+// ---- checked build ------------------------------------------------------------------------------
+// With -DDS_BOUNDS_CHECK every global load of x, of the packed weights and of the residual, and every
+// global store, first tests its address against the extent the host derived from the call's
+// arguments.  An access outside is NOT performed; the first one leaves a site code in a status word
+// (ds_bounds_status).  Nothing traps.  Without the flag the tests compile to nothing.
+#ifdef DS_BOUNDS_CHECK
+__device__ __forceinline__ bool bounds_ok(int* status, const void* base, long long total, const void* ptr, int bytes,
+                                          int site)
+{
+    const char* b = static_cast<const char*>(base);
+    const char* q = static_cast<const char*>(ptr);
+    if (q >= b && q + bytes <= b + total) return true;
+    if (status) atomicCAS(status, 0, site);
+    return false;
+}
+#define DS_X_OK(p, ptr, bytes) bounds_ok((p).chk_status, (p).x, (p).chk_x_bytes, ptr, bytes, 1)
+#define DS_W_OK(p, ptr, bytes) bounds_ok((p).chk_status, (p).packed, (p).chk_w_bytes, ptr, bytes, 2)
+#define DS_O_OK(p, base, ptr, bytes) bounds_ok((p).chk_status, base, (p).chk_o_bytes, ptr, bytes, 3)
+#else
+#define DS_X_OK(p, ptr, bytes) true
+#define DS_W_OK(p, ptr, bytes) true
+#define DS_O_OK(p, base, ptr, bytes) true
+#endif
+int* bounds_status_ptr();  // device address of the status word (ds_gemm_ws.cu), null on failure
 
 __device__ __forceinline__ void red_shared_add(int* addr, int v)
 {
@@ -130,7 +159,8 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
     auto finish = [&](int v, long long oidx) -> int {
         if (p.residual) {
             // fp32 add of the two values as the reference's `out += identity` does it.
-            v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + oidx)));
+            const int r = DS_O_OK(p, p.residual, p.residual + oidx, 4) ? __ldg(p.residual + oidx) : 0;
+            v = __float2int_rn(__int2float_rn(v) + __int2float_rn(r));
         }
         if (p.relu) v = max(v, 0);
         if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi) * p.rq_mul + p.rq_add;
@@ -162,11 +192,11 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
 #pragma unroll
                     for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j, o + i) + addc[j], o + i);
                     if (p.out_kind == DS_OUT_I32) {
-                        *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
-                        if (p.operand_out)
+                        if (DS_O_OK(p, oi, oi + o, 16)) *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
+                        if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o, 16))
                             *reinterpret_cast<float4*>(p.operand_out + o) =
                                 make_float4(operand(v[0]), operand(v[1]), operand(v[2]), operand(v[3]));
-                    } else {
+                    } else if (DS_O_OK(p, of, of + o, 16)) {
                         *reinterpret_cast<float4*>(of + o) =
                             make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
                                         __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
@@ -185,9 +215,9 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                         const long long o = ((long long)b * p.OC + n) * p.P + pp;
                         const int v = finish(accv(4 * h + i, j, o) + addc[j], o);
                         if (p.out_kind == DS_OUT_I32) {
-                            oi[o] = v;
-                            if (p.operand_out) p.operand_out[o] = operand(v);
-                        } else {
+                            if (DS_O_OK(p, oi, oi + o, 4)) oi[o] = v;
+                            if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o, 4)) p.operand_out[o] = operand(v);
+                        } else if (DS_O_OK(p, of, of + o, 4)) {
                             of[o] = __int2float_rn(v) * p.inv_scale;
                         }
                     }
@@ -209,11 +239,11 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
 #pragma unroll
                     for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j, o + j) + addc[4 * h + j], o + j);
                     if (p.out_kind == DS_OUT_I32) {
-                        *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
-                        if (p.operand_out)
+                        if (DS_O_OK(p, oi, oi + o, 16)) *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
+                        if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o, 16))
                             *reinterpret_cast<float4*>(p.operand_out + o) =
                                 make_float4(operand(v[0]), operand(v[1]), operand(v[2]), operand(v[3]));
-                    } else {
+                    } else if (DS_O_OK(p, of, of + o, 16)) {
                         *reinterpret_cast<float4*>(of + o) =
                             make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
                                         __int2float_rn(v[2]) * p.inv_scale, __int2float_rn(v[3]) * p.inv_scale);
@@ -224,9 +254,10 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                         if (n + j >= p.N) continue;
                         const int v = finish(accv(i, 4 * h + j, o + j) + addc[4 * h + j], o + j);
                         if (p.out_kind == DS_OUT_I32) {
-                            oi[o + j] = v;
-                            if (p.operand_out) p.operand_out[o + j] = operand(v);
-                        } else {
+                            if (DS_O_OK(p, oi, oi + o + j, 4)) oi[o + j] = v;
+                            if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o + j, 4))
+                                p.operand_out[o + j] = operand(v);
+                        } else if (DS_O_OK(p, of, of + o + j, 4)) {
                             of[o + j] = __int2float_rn(v) * p.inv_scale;
                         }
                     }
@@ -263,7 +294,8 @@ __device__ __forceinline__ void reduce_tile(const GemmParams& p, int m0, int n0,
         for (int j = 0; j < TN; ++j) {
             const int n = n0 + ncol(j);
             if (n >= p.N) continue;
-            atomicAdd(oi + rowoff + n * nstride, accv(i, j, 0) + colc(ncol(j)));
+            if (DS_O_OK(p, oi, oi + rowoff + n * nstride, 4))
+                atomicAdd(oi + rowoff + n * nstride, accv(i, j, 0) + colc(ncol(j)));
         }
     }
 }

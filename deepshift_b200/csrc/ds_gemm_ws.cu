@@ -6,12 +6,16 @@
 namespace ds {
 
 int* kernel_error_flag();
+int* bounds_status_ptr();
 
 namespace {
 
 __device__ int g_ws_error = 0;  // never set in a correct run
 
 int* g_ws_error_ptr[kMaxDevices];  // device address of the flag, looked up once per device
+
+__device__ int g_bounds_status = 0;  // checked build: site code of the first access outside its extent
+int* g_bounds_status_ptr[kMaxDevices];
 
 }  // namespace
 
@@ -28,6 +32,25 @@ int* kernel_error_flag()
         g_ws_error_ptr[dev] = static_cast<int*>(ptr);
     }
     return g_ws_error_ptr[dev];
+}
+
+int* bounds_status_ptr()
+{
+#ifdef DS_BOUNDS_CHECK
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!g_bounds_status_ptr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_bounds_status) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        g_bounds_status_ptr[dev] = static_cast<int*>(ptr);
+    }
+    return g_bounds_status_ptr[dev];
+#else
+    return nullptr;
+#endif
 }
 
 int launch_ws(const GemmParams& p0, int am, cudaStream_t st)
@@ -61,5 +84,25 @@ extern "C" int ds_last_kernel_error(int* flag)
     const int zero = 0;
     if (v && cudaMemcpyToSymbol(ds::g_ws_error, &zero, sizeof(int)) != cudaSuccess) return DS_ERR_CUDA;
     *flag = v;
+    return DS_OK;
+}
+
+// Checked build (-DDS_BOUNDS_CHECK): reads and clears the status word; *status = 0 means every
+// access stayed inside its extent, 1 / 2 / 3 name the first offender (activations, packed weights,
+// output or residual).  Synchronises the device.  A normal build reports 0 and *checked = 0.
+extern "C" int ds_bounds_status(int* status, int* checked)
+{
+    if (!status) return DS_ERR_BAD_ARG;
+    *status = 0;
+#ifdef DS_BOUNDS_CHECK
+    if (checked) *checked = 1;
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, ds::g_bounds_status, sizeof(int)) != cudaSuccess) return DS_ERR_CUDA;
+    const int zero = 0;
+    if (v && cudaMemcpyToSymbol(ds::g_bounds_status, &zero, sizeof(int)) != cudaSuccess) return DS_ERR_CUDA;
+    *status = v;
+#else
+    if (checked) *checked = 0;
+#endif
     return DS_OK;
 }

@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 for (int e = 0; e < EW; ++e) {
                     const int jw = (pt + e * WS_PROD) / BN;
                     uint32_t w = 0;
-                    if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len) w = uint32_t(__ldg(wrow + w0 + jw));
+                    if (wrow && jw < p.kt_words && w0 + jw < p.dec.row_len && DS_W_OK(p, wrow + w0 + jw, 4)) w = uint32_t(__ldg(wrow + w0 + jw));
                     w_reg[e] = w;
                 }
             }
@@ -349,9 +349,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     int4 c = make_int4(padv, padv, padv, padv);
                     int l = padv, r = padv;
                     if ((rowmask[0] >> e.y) & 1u) {  // rows past the tile: kh = 31
-                        c = __ldg(reinterpret_cast<const int4*>(rowp));
-                        if (colmask[0] & 1u) l = __ldg(rowp - 1);
-                        if (colmask[0] & 2u) r = __ldg(rowp + 4);
+                        if (DS_X_OK(p, rowp, 16)) c = __ldg(reinterpret_cast<const int4*>(rowp));
+                        if ((colmask[0] & 1u) && DS_X_OK(p, rowp - 1, 4)) l = __ldg(rowp - 1);
+                        if ((colmask[0] & 2u) && DS_X_OK(p, rowp + 4, 4)) r = __ldg(rowp + 4);
                     }
                     xr[6 * j + 0] = l;
                     xr[6 * j + 1] = c.x;
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     int4 c = make_int4(padv, padv, padv, padv);
-                    if (rv && ((colmask[0] >> v) & 1u)) c = __ldg(rowp + v);
+                    if (rv && ((colmask[0] >> v) & 1u) && DS_X_OK(p, rowp + v, 16)) c = __ldg(rowp + v);
                     xr[4 * v + 0] = c.x;
                     xr[4 * v + 1] = c.y;
                     xr[4 * v + 2] = c.z;
@@ -383,9 +383,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     int2 c = make_int2(padv, padv);
                     int l = padv, r = padv;
                     if ((rowmask[0] >> e.y) & 1u) {  // rows past the tile: kh = 31
-                        c = __ldg(reinterpret_cast<const int2*>(rowp));
-                        if (colmask[0] & 1u) l = __ldg(rowp - 1);
-                        if (colmask[0] & 2u) r = __ldg(rowp + 2);
+                        if (DS_X_OK(p, rowp, 8)) c = __ldg(reinterpret_cast<const int2*>(rowp));
+                        if ((colmask[0] & 1u) && DS_X_OK(p, rowp - 1, 4)) l = __ldg(rowp - 1);
+                        if ((colmask[0] & 2u) && DS_X_OK(p, rowp + 2, 4)) r = __ldg(rowp + 2);
                     }
                     xr[4 * j + 0] = l;
                     xr[4 * j + 1] = c.x;
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 #pragma unroll
                         for (int kw = 0; kw < KW; ++kw) {
                             int val = padv;
-                            if (rv && (colmask[q] & (1u << kw))) val = __ldg(rowp + kw);
+                            if (rv && (colmask[q] & (1u << kw)) && DS_X_OK(p, rowp + kw, 4)) val = __ldg(rowp + kw);
                             xr[(q * RMAX + u) * KW + kw] = val;
                         }
                     }
@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 #pragma unroll
                     for (int q = 0; q < PIX; ++q) {
                         int val = padv;
-                        if (((rowmask[q] >> e.y) & (colmask[q] >> e.z) & 1u) != 0u)
+                        if (((rowmask[q] >> e.y) & (colmask[q] >> e.z) & 1u) != 0u && DS_X_OK(p, x_pix[q] + e.x, 4))
                             val = __ldg(reinterpret_cast<const int*>(x_pix[q] + e.x));
                         xr[q * WS_BKT + u] = val;
                     }
@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
 #pragma unroll
                 for (int v = 0; v < WS_BKT / 4; ++v) {
                     int4 c = make_int4(padv, padv, padv, padv);
-                    if (rowmask[0] && 4 * v < p.bk && k0 + 4 * v < p.K) c = __ldg(rp + v);
+                    if (rowmask[0] && 4 * v < p.bk && k0 + 4 * v < p.K && DS_X_OK(p, rp + v, 16)) c = __ldg(rp + v);
                     xr[4 * v + 0] = c.x;
                     xr[4 * v + 1] = c.y;
                     xr[4 * v + 2] = c.z;

@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
 #pragma unroll
             for (int m = 0; m < MR; ++m) {
                 int4 r = make_int4(0, 0, 0, 0);
-                if (m0 + m < p.M) r = __ldg(reinterpret_cast<const int4*>(xi + (size_t)(m0 + m) * p.K + k0));
+                if (m0 + m < p.M && DS_X_OK(p, xi + (size_t)(m0 + m) * p.K + k0, 16))
+                    r = __ldg(reinterpret_cast<const int4*>(xi + (size_t)(m0 + m) * p.K + k0));
                 xv[m][0] = __float_as_int(operand_of<false, INK>(p, r.x));
                 xv[m][1] = __float_as_int(operand_of<false, INK>(p, r.y));
                 xv[m][2] = __float_as_int(operand_of<false, INK>(p, r.z));
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
 #pragma unroll
             for (int m = 0; m < MR; ++m) {
                 xv[m] = 0;
-                if (m0 + m < p.M)
+                if (m0 + m < p.M && DS_X_OK(p, xi + (size_t)(m0 + m) * p.K + k, 4))
                     xv[m] = __float_as_int(operand_of<false, INK>(p, __ldg(xi + (size_t)(m0 + m) * p.K + k)));
             }
 #pragma unroll
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
 #pragma unroll
                 for (int c = 0; c < CN; ++c) {
                     wq[c] = make_uint4(0, 0, 0, 0);
-                    if (n0 + c < p.N)
+                    if (n0 + c < p.N && DS_W_OK(p, reinterpret_cast<const uint4*>(p.packed + (size_t)(n0 + c) * p.dec.row_len) + q, 16))
                         wq[c] = __ldg(reinterpret_cast<const uint4*>(p.packed + (size_t)(n0 + c) * p.dec.row_len) + q);
                 }
 #pragma unroll
@@ -122,7 +123,8 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
                 uint32_t word[CN];
 #pragma unroll
                 for (int c = 0; c < CN; ++c)
-                    word[c] = (n0 + c < p.N) ? uint32_t(__ldg(p.packed + (size_t)(n0 + c) * p.dec.row_len + w)) : 0u;
+                    word[c] = (n0 + c < p.N && DS_W_OK(p, p.packed + (size_t)(n0 + c) * p.dec.row_len + w, 4))
+                                  ? uint32_t(__ldg(p.packed + (size_t)(n0 + c) * p.dec.row_len + w)) : 0u;
                 word_step(w, word);
             }
         }
@@ -167,10 +169,12 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
             const size_t o = (size_t)row * p.N + n;
             int v = acc[m][c];
             if (p.bias) v += __ldg(p.bias + n);
-            if (p.residual) v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + o)));
+            if (p.residual && DS_O_OK(p, p.residual, p.residual + o, 4))
+                v = __float2int_rn(__int2float_rn(v) + __int2float_rn(__ldg(p.residual + o)));
             if (p.relu) v = max(v, 0);
             if (p.requant) v = min(max(v, p.rq_lo), p.rq_hi) * p.rq_mul + p.rq_add;
             if (p.round_f32) v = __float2int_rn(__int2float_rn(v));
+            if (!DS_O_OK(p, p.out, static_cast<int*>(p.out) + o, 4)) continue;
             if (p.out_kind == DS_OUT_I32) static_cast<int*>(p.out)[o] = v;
             else static_cast<float*>(p.out)[o] = __int2float_rn(v) * p.inv_scale;
         }

@@ -324,11 +324,39 @@ int ds_maxpool_nhwc(const int32_t *x, int B, int H, int W, int C, int k, int str
 int ds_avgpool_fix_nhwc(const int32_t *x, int32_t *out, int B, int H, int W, int C, int F, void *stream);
 
 /*
+ * The reference's "unoptimized" fp32 baseline (pytorch/unoptimized/kernels/cuda/unoptimized.cu:63-103
+ * GEMM, :10-61 IM2COL / COL2IM; entry points unoptimized_cuda.cpp:24-56): ordinary multiply-accumulate
+ * layers at the same (deliberately low) level of tuning as its shift kernels, for the latency
+ * comparison of its README.  weight is [N][K] / [OC][C][KH][KW] fp32, bias may be NULL, out is
+ * [M][N] / NCHW fp32; the convolution reads the unpadded input.
+ */
+int ds_unopt_linear_f32(const float *x, const float *weight, const float *bias, float *out, int M, int K,
+                        int N, void *stream);
+int ds_unopt_conv2d_f32(const float *x, const float *weight, const float *bias, float *out, int B, int C,
+                        int H, int W, int OC, int KH, int KW, int sh, int sw, int ph, int pw, void *stream);
+
+/*
  * Reads and clears the device-side flag that a kernel of this library sets when one of its
  * bounded waits ran out (its output is then undefined; it never happens in a correct run).
  * Synchronises the current device.  *flag = 0 means no error.
  */
 int ds_last_kernel_error(int *flag);
+
+/*
+ * Checked build.  The library compiled with -DDS_BOUNDS_CHECK (deepshift_b200/_build.py, flavour
+ * "checked": libdeepshift_b200_checked.so) tests the address of every global load of activations,
+ * packed weights and residual and of every global store in the linear / convolution kernels against
+ * the extents implied by the call's arguments.  An access outside is skipped, never performed, and
+ * the first one leaves its kind in a status word: 1 activations, 2 packed weights, 3 output /
+ * residual / operand_out.  Nothing traps.  (The TMA-fed staged kernel is not instrumented: the
+ * tensor map bounds its loads in hardware.)
+ *   ds_bounds_status        reads and clears the status word (synchronises the device); *checked
+ *                           says whether this library was built with the checks.
+ *   ds_bounds_debug_shrink_x  checked build only: declares x `bytes` shorter than it is, so that the
+ *                           checks can be seen to fire without anything leaving a real buffer.
+ */
+int ds_bounds_status(int *status, int *checked);
+int ds_bounds_debug_shrink_x(long long bytes);
 
 /*
  * Number of kernels this library has launched in this process so far (a host-side counter;

@@ -221,3 +221,21 @@ def test_staged_convolution_stays_inside_its_buffers(oracle, cuda_device, case):
     assert codes.intact() and nchw.intact() and nxt_f.intact() and wsf.intact() and xs_f.intact() and pf.intact()
     assert bf.intact() and wf.intact()
     assert int(wsf.t[:16383].abs().sum()) == 0
+
+
+def test_bounds_checking_flavour_of_the_library(cuda_device):
+    """The library built with -DDS_BOUNDS_CHECK (every global access of the linear / convolution
+    kernels tests its address first, skips it if outside and records the kind) in a process of its
+    own: all shapes exact with status 0, and the checks are seen to fire when the activations are
+    declared shorter than they are.  Nothing traps and nothing leaves a real buffer."""
+    import os
+    import subprocess
+    import sys
+    from deepshift_b200 import _build
+    if not os.path.exists(_build.CHECKED_LIB_PATH) and _build.nvcc_path() is None:
+        pytest.skip("checked flavour not built and no nvcc here")
+    env = dict(os.environ, DEEPSHIFT_B200_CHECKED="1")
+    script = os.path.join(os.path.dirname(os.path.abspath(__file__)), "checked_build_cases.py")
+    res = subprocess.run([sys.executable, script], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         timeout=1200)
+    assert res.returncode == 0 and "checked build: ok" in res.stdout, res.stdout[-3000:]
