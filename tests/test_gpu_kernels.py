@@ -962,26 +962,26 @@ def test_act_bits_auto_picks_the_path_by_looking_at_the_data(oracle, cuda_device
 
 
 def test_unoptimized_fp32_baseline_matches_torch(cuda_device):
-    """The reference's fp32 strawman (unoptimized/): results agree with torch.nn.functional to fp32
-    rounding (tolerance 1e-4 of the largest output: sums of a few hundred products, summed in a
-    different order than cuDNN / cuBLAS)."""
+    """The reference's fp32 strawman (unoptimized/): results agree with a float64 evaluation of
+    torch.nn.functional to fp32 rounding (tolerance 1e-5 of the largest output: sums of a few hundred
+    products)."""
     from deepshift_b200 import unoptimized as U
     torch.manual_seed(5)
     for (B, C, H, W, OC, k, s, p) in [(2, 3, 17, 13, 20, 3, 1, 1), (3, 8, 9, 9, 33, 5, 2, 2), (2, 16, 7, 7, 40, 1, 1, 0)]:
         x = torch.randn(B, C, H, W, device=cuda_device)
         w = torch.randn(OC, C, k, k, device=cuda_device) * 0.1
         b = torch.randn(OC, device=cuda_device)
-        ref = torch.nn.functional.conv2d(x, w, b, s, p)
+        ref = torch.nn.functional.conv2d(x.double(), w.double(), b.double(), s, p)   # float64: torch's fp32 path may use TF32
         got = U.conv2d(x, w, b, (s, s), (p, p))
-        assert got.shape == ref.shape and float((got - ref).abs().max()) <= 1e-4 * float(ref.abs().max())
+        assert got.shape == ref.shape and float((got.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
     x, w = torch.randn(70, 301, device=cuda_device), torch.randn(45, 301, device=cuda_device)
-    ref = torch.nn.functional.linear(x, w)
-    assert float((U.linear(x, w, None) - ref).abs().max()) <= 1e-4 * float(ref.abs().max())
+    ref = torch.nn.functional.linear(x.double(), w.double())
+    assert float((U.linear(x, w, None).double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
     model = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.ReLU(), torch.nn.Flatten(),
                                 torch.nn.Linear(8 * 6 * 6, 10)).to(cuda_device)
     xin = torch.randn(4, 3, 6, 6, device=cuda_device)
     with torch.no_grad():
-        want = model(xin)
-        got = U.convert_to_unoptimized(model)(xin)
+        want = model.double()(xin.double())
+        got = U.convert_to_unoptimized(model.float())(xin)
     assert isinstance(model[0], U.UnoptimizedConv2d) and isinstance(model[3], U.UnoptimizedLinear)
-    assert float((got - want).abs().max()) <= 1e-4 * float(want.abs().max())
+    assert float((got.double() - want).abs().max()) <= 1e-5 * float(want.abs().max())
