@@ -23,7 +23,6 @@ class Fuse(ctypes.Structure):
         ("round_f32", ctypes.c_int), ("reserved", ctypes.c_int * 3),
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_longlong),
         ("prepared", ctypes.c_void_p), ("prepared_bytes", ctypes.c_longlong),
-        ("operand_out", ctypes.c_void_p),
     ]
 
 
@@ -43,7 +42,7 @@ class StagedOut(ctypes.Structure):
     ]
 
 
-IN_I32, IN_F32_CONV, IN_F32_LINEAR, IN_I32_CLAMP, IN_OPERAND_F32 = 0, 1, 2, 3, 4
+IN_I32, IN_F32_CONV, IN_F32_LINEAR, IN_I32_CLAMP = 0, 1, 2, 3
 OUT_I32, OUT_F32 = 0, 1
 
 _VP, _I, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
@@ -57,8 +56,6 @@ _SIGNATURES = {
     "ds_compress": [_VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "ds_quantize_f32": [_VP, _VP, _LL, _I, _I, _I, _VP],
     "ds_maxpool2d_i32": [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
-    "ds_maxpool2d_i32_operand": [_VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
-    "ds_quantize_operand_f32": [_VP, _VP, _LL, _I, _I, _VP],
     "ds_avgpool_fix_i32": [_VP, _VP, _I, _I, _I, _I, _I, _VP],
     "ds_pipe_peak": [_I, _I, ctypes.POINTER(ctypes.c_double), _VP],
     "ds_last_kernel_error": [ctypes.POINTER(ctypes.c_int)],

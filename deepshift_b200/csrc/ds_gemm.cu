@@ -470,7 +470,7 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     if (gx > 2147483647LL || gy > 65535) return DS_ERR_RANGE;
     p.splits = 1;
     p.tiles_per_split = p.ntiles;
-    const bool plain = p.out_kind == DS_OUT_I32 && !p.relu && !p.requant && !p.round_f32 && !p.residual && !p.operand_out;
+    const bool plain = p.out_kind == DS_OUT_I32 && !p.relu && !p.requant && !p.round_f32 && !p.residual;
     if (MODE == MODE_INT && AM == AM_LINEAR && plain && !p.gate && gx * gy < 148) {
         // Few output tiles (small batch): split K across gridDim.z until two CTAs per SM have work;
         // the partial sums meet through integer atomics in the zeroed output.
@@ -566,17 +566,12 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.dec.row_len = (p.K + p.dec.num - 1) / p.dec.num;
     ds_fuse_t f = {};
     if (fuse) f = *fuse;
-    if (f.in_kind < 0 || f.in_kind > 4 || f.out_kind < 0 || f.out_kind > 1) return DS_ERR_BAD_ARG;
+    if (f.in_kind < 0 || f.in_kind > 3 || f.out_kind < 0 || f.out_kind > 1) return DS_ERR_BAD_ARG;
     const int I = f.act_integer_bits, F = f.act_fraction_bits;
-    const bool in_operand = f.in_kind == DS_IN_OPERAND_F32;
     const bool in_clamp = f.in_kind == DS_IN_I32_CLAMP;
-    if (f.operand_out && (f.out_kind != DS_OUT_I32 || (reinterpret_cast<uintptr_t>(f.operand_out) & 15u)))
-        return DS_ERR_BAD_ARG;
-    p.operand_out = f.operand_out;
     const bool needs_if = f.in_kind != DS_IN_I32 || f.out_kind != DS_OUT_I32 || f.requant;
     if (needs_if && (F < 0 || F > 30)) return DS_ERR_BAD_ARG;
     if ((f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp) && (I < 1 || I + F > 32)) return DS_ERR_BAD_ARG;
-    if ((in_operand || f.operand_out) && (I < 1 || F > 16 || (I == 1 ? F + 2 : I + F) > 18)) return DS_ERR_BAD_ARG;
     p.in_kind = f.in_kind;
     p.out_kind = f.out_kind;
     p.relu = f.relu;
@@ -607,7 +602,7 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
     p.residual = f.residual;
     p.q.scale = float(1ll << (needs_if ? F : 0));
     p.inv_scale = 1.0f / p.q.scale;
-    const bool uses_rtf = f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp || in_operand || f.operand_out != nullptr;
+    const bool uses_rtf = f.in_kind == DS_IN_F32_CONV || f.requant || in_clamp;
     const bool sign_mode = uses_rtf && I == 1;  // round_to_fixed(x, 1, F) = sign(x) - 1
     p.q.sign_mode = sign_mode ? 1 : 0;
     p.q.lo = p.q.hi = 0.f;
@@ -628,13 +623,12 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.rq_hi = int(hi);
     }
     p.pad_raw = (f.in_kind == DS_IN_I32) ? 0 : (in_clamp ? (sign_mode ? 1 : 0) : kPadMarker);
-    if (in_operand) p.pad_raw = 0x3F000000;  // 0.5f: the operand of the code 0
     p.in_mul2 = int(2u * unsigned(p.rq_mul));
     p.in_add2 = int(2u * unsigned(p.rq_add) + unsigned(kHalfMagicBits + 1));
     // FP32-pipe path: needs base == 0, every |x| <= 2^(act_bits-1) <= 2^17, and room for at
     // least one k-tile of terms (each of magnitude <= 2^(act_bits-1) + 1) between drains.
     int ab = f.act_bits == DS_ACT_BITS_AUTO ? 0 : f.act_bits;
-    if (f.in_kind == DS_IN_F32_CONV || in_clamp || in_operand) ab = sign_mode ? F + 2 : I + F;
+    if (f.in_kind == DS_IN_F32_CONV || in_clamp) ab = sign_mode ? F + 2 : I + F;
     if (f.in_kind == DS_IN_F32_LINEAR) ab = 0;
     use_fp = (base == 0 && ab >= 1 && ab <= 18);
     p.flush_tiles = 0;
@@ -644,7 +638,6 @@ int setup_common(GemmParams& p, int bits, int base, const ds_fuse_t* fuse, bool&
         p.flush_tiles = int(terms > (1 << 20) ? (1 << 20) : terms);  // divided by bk at launch
         if (terms < 28) use_fp = false;
     }
-    if (in_operand && !use_fp) return DS_ERR_UNSUPPORTED;  // the operand form exists for the FP32-pipe path only
     return DS_OK;
 }
 
@@ -755,12 +748,10 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     // Small batches run on the integer pipe: up to 16 rows on the kernel that splits K across the
     // lanes of a warp, up to 64 rows on the block kernel with a 64-row tile (K split across CTAs
     // when nothing is fused into the epilogue).
-    if (p.in_kind != DS_IN_OPERAND_F32 && !p.operand_out) {
-        if (M <= 16) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
-        if (M <= 64) {
-            const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_INT, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
-            if (rc != DS_ERR_UNSUPPORTED) return rc;
-        }
+    if (M <= 16) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
+    if (M <= 64) {
+        const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_INT, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
+        if (rc != DS_ERR_UNSUPPORTED) return rc;
     }
     return launch_am<AM_LINEAR>(p, fp, static_cast<cudaStream_t>(stream));
 }

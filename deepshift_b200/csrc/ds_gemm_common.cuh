@@ -29,7 +29,6 @@ struct GemmParams {
     const int32_t* bias;  // may be null
     void* out;            // int32 or fp32
     const int32_t* residual;
-    float* operand_out;   // second output: clamp(v) + 0.5 for the next layer's staging code, or null
     int M, K, N;
     Decode dec;
     int kt_words;     // packed words per row per k-tile
@@ -69,7 +68,7 @@ struct GemmParams {
     const int* gate;
     int gate_want;
     // Checked build (-DDS_BOUNDS_CHECK) only: byte extents of x, of the packed weights and of the output
-    // (residual and operand_out have the output's element count), and where the first violation goes.
+    // (the residual has the output's element count), and where the first violation goes.
     long long chk_x_bytes, chk_w_bytes, chk_o_bytes;
     int* chk_status;
     // weights expanded ahead of time by the caller (ds_conv2d_prepare)
@@ -167,10 +166,6 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
         if (p.round_f32) v = __float2int_rn(__int2float_rn(v));
         return v;
     };
-    // the next layer's quantiser on the finished code, + 0.5 (see GemmParams::rq_*)
-    auto operand = [&](int v) -> float {
-        return __int2float_rn(min(max(v, p.rq_lo), p.rq_hi) * p.rq_mul + p.rq_add) + 0.5f;
-    };
     int32_t* oi = static_cast<int32_t*>(p.out);
     float* of = static_cast<float*>(p.out);
 
@@ -193,9 +188,6 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                     for (int i = 0; i < 4; ++i) v[i] = finish(accv(4 * h + i, j, o + i) + addc[j], o + i);
                     if (p.out_kind == DS_OUT_I32) {
                         if (DS_O_OK(p, oi, oi + o, 16)) *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
-                        if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o, 16))
-                            *reinterpret_cast<float4*>(p.operand_out + o) =
-                                make_float4(operand(v[0]), operand(v[1]), operand(v[2]), operand(v[3]));
                     } else if (DS_O_OK(p, of, of + o, 16)) {
                         *reinterpret_cast<float4*>(of + o) =
                             make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
@@ -216,7 +208,6 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                         const int v = finish(accv(4 * h + i, j, o) + addc[j], o);
                         if (p.out_kind == DS_OUT_I32) {
                             if (DS_O_OK(p, oi, oi + o, 4)) oi[o] = v;
-                            if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o, 4)) p.operand_out[o] = operand(v);
                         } else if (DS_O_OK(p, of, of + o, 4)) {
                             of[o] = __int2float_rn(v) * p.inv_scale;
                         }
@@ -240,9 +231,6 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                     for (int j = 0; j < 4; ++j) v[j] = finish(accv(i, 4 * h + j, o + j) + addc[4 * h + j], o + j);
                     if (p.out_kind == DS_OUT_I32) {
                         if (DS_O_OK(p, oi, oi + o, 16)) *reinterpret_cast<int4*>(oi + o) = make_int4(v[0], v[1], v[2], v[3]);
-                        if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o, 16))
-                            *reinterpret_cast<float4*>(p.operand_out + o) =
-                                make_float4(operand(v[0]), operand(v[1]), operand(v[2]), operand(v[3]));
                     } else if (DS_O_OK(p, of, of + o, 16)) {
                         *reinterpret_cast<float4*>(of + o) =
                             make_float4(__int2float_rn(v[0]) * p.inv_scale, __int2float_rn(v[1]) * p.inv_scale,
@@ -255,8 +243,6 @@ __device__ __forceinline__ void store_tile(const GemmParams& p, int m0, int n0, 
                         const int v = finish(accv(i, 4 * h + j, o + j) + addc[4 * h + j], o + j);
                         if (p.out_kind == DS_OUT_I32) {
                             if (DS_O_OK(p, oi, oi + o + j, 4)) oi[o + j] = v;
-                            if (p.operand_out && DS_O_OK(p, p.operand_out, p.operand_out + o + j, 4))
-                                p.operand_out[o + j] = operand(v);
                         } else if (DS_O_OK(p, of, of + o + j, 4)) {
                             of[o + j] = __int2float_rn(v) * p.inv_scale;
                         }
@@ -303,12 +289,11 @@ __device__ __forceinline__ void reduce_tile(const GemmParams& p, int m0, int n0,
 // Fixed-point value v (int32 bits, or fp32 bits for the fp32 input kinds) as the operand the
 // kernels keep in shared memory: x + 0.5 as a float on the FP path, x as int bits otherwise.
 // INK selects the input kind at compile time: INK_I32, INK_I32_CLAMP or INK_F32 (either fp32 kind).
-constexpr int INK_I32 = 0, INK_F32 = 1, INK_I32_CLAMP = 2, INK_OPERAND = 3;  // INK_OPERAND: x + 0.5 as fp32 already
+constexpr int INK_I32 = 0, INK_F32 = 1, INK_I32_CLAMP = 2;
 
 template <bool FP, int INK>
 __device__ __forceinline__ float operand_of(const GemmParams& p, int v)
 {
-    if (INK == INK_OPERAND) return __int_as_float(v);  // FP path only
     if (INK == INK_I32_CLAMP) {
         const int c = min(max(v, p.rq_lo), p.rq_hi);
         if (FP) return __int_as_float(c * p.in_mul2 + p.in_add2) - kHalfMagic;
@@ -330,8 +315,7 @@ __device__ __forceinline__ float operand_of(const GemmParams& p, int v)
 template <class Fn>
 __device__ __forceinline__ void with_input_kind(const GemmParams& p, Fn fn)
 {
-    if (p.in_kind == DS_IN_OPERAND_F32) fn(std::integral_constant<int, INK_OPERAND>());
-    else if (p.in_kind == DS_IN_I32) fn(std::integral_constant<int, INK_I32>());
+    if (p.in_kind == DS_IN_I32) fn(std::integral_constant<int, INK_I32>());
     else if (p.in_kind == DS_IN_I32_CLAMP) fn(std::integral_constant<int, INK_I32_CLAMP>());
     else fn(std::integral_constant<int, INK_F32>());
 }

@@ -90,21 +90,28 @@ __device__ __forceinline__ void warp_arrive(unsigned long long* bar)
 // suspend the thread for up to WS_WAIT_NS before it reports "not yet", so a waiting warp issues
 // almost nothing.  Returns false after WS_WAIT_LIMIT such rounds (seconds; a correct run waits
 // microseconds).
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, bool gave_up = false)
+__device__ __forceinline__ bool mbar_try_once(unsigned addr, unsigned parity)
+{
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity), "r"(WS_WAIT_NS)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  `err` is the CTA's error word in shared memory: whoever gives up sets it, and every
+// wait that finds it set after a failed round gives up at once, so that a launch in which something
+// went wrong ends within seconds instead of one full limit per wait.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* err)
 {
     const unsigned addr = smem_u32(bar);
-    // A thread that has given up once makes its later waits short (one round), so that a launch in
-    // which something went wrong still ends within seconds instead of one full limit per wait.
-    const int limit = gave_up ? 1 : WS_WAIT_LIMIT;
-    for (int i = 0; i < limit; ++i) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity), "r"(WS_WAIT_NS)
-            : "memory");
-        if (ok) return true;
+    for (int i = 0; i < WS_WAIT_LIMIT; ++i) {
+        if (mbar_try_once(addr, parity)) return true;
+        if (*err) return false;
     }
+    *err = 1;
     return false;
 }
 
@@ -567,7 +574,6 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // stores -- also across item boundaries: while the consumers finish an output tile and run
         // its epilogue, the first k-tiles of the next item are already being staged.
         int item = blockIdx.x, seq = 0, git = 0;
-        bool pbad = false;
         if (item < total_items) {
             WsItem cur = ws_item(p, item, BM, BN);
             int tile = cur.t_begin;
@@ -577,10 +583,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             issue_loads(tile, cur.m0);
             while (true) {
                 const int st = git % WS_STAGES;
-                if (git >= WS_STAGES && !mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u, pbad)) {
-                    pbad = true;
-                    s.err = 1;
-                }
+                if (git >= WS_STAGES) mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u, &s.err);
                 const int k0 = tile * p.bk;
                 // Expanded weights are 0 beyond K, so the x values stored there need no care.
                 const bool last = !PRE && tile + 1 >= p.ntiles;
@@ -637,7 +640,6 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         tm = (warp / WNG) * 4 + (lane >> 3);
     }
     float accf[kTM][TN];
-    bool bad = false;
     int git = 0, seq = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++seq) {
         const WsItem cur = ws_item(p, item, BM, BN);
@@ -649,7 +651,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         int ndrains = 0, since = 0;
         for (int it = 0; it < my_tiles; ++it, ++git) {
             const int st = git % WS_STAGES;
-            if (!mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u, bad)) bad = true;
+            mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u, &s.err);
             // The k-tile sizes of 3x3, 1x1 / 7x7 and 5x5 windows get fully unrolled loops.
             auto k_loop = [&](auto bk_tag) {
                 constexpr int CBK = decltype(bk_tag)::value;
@@ -784,7 +786,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
         }
     }
-    if (bad) *p.err_flag = 1;
+    if (s.err) *p.err_flag = 1;
 }
 
 // Expands the packed weights of one launch into floats laid out as the k-tiles want them:

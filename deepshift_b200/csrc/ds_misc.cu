@@ -45,29 +45,11 @@ __global__ void quantize_kernel(const float* __restrict__ x, int32_t* __restrict
     }
 }
 
-__global__ void quantize_operand_kernel(const float* __restrict__ x, float* __restrict__ out, long long n, Quant q)
-{
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-         i += (long long)gridDim.x * blockDim.x)
-        out[i] = quant_conv_f(__ldg(x + i), q) + 0.5f;
-}
-
-// round_to_fixed on an int32 code (clamp, or the sign rule for one integer bit), + 0.5 as fp32.
-struct OperandQuant {
-    int lo, hi, mul, add;
-};
-
-__device__ __forceinline__ float operand_of_code(int v, const OperandQuant& q)
-{
-    return __int2float_rn(min(max(v, q.lo), q.hi) * q.mul + q.add) + 0.5f;
-}
-
 // Max pooling on int32 NCHW; positions outside the image do not take part (as with
 // torch.nn.functional.max_pool2d's implicit -inf padding).  Monotone, hence identical to pooling
 // the fp32 values int / 2^F and converting back.
 __global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out, long long total, int H,
-                               int W, int OH, int OW, int k, int st, int pad, float* __restrict__ operand,
-                               OperandQuant oq)
+                               int W, int OH, int OW, int k, int st, int pad)
 {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
@@ -86,7 +68,6 @@ __global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restric
             }
         }
         out[i] = best;
-        if (operand) operand[i] = operand_of_code(best, oq);
     }
 }
 
@@ -94,8 +75,7 @@ __global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restric
 // tensors are 16-byte aligned: a thread produces four neighbouring outputs from, per input row,
 // two 16-byte loads and the one value to their left (9 loads instead of 36), one 16-byte store.
 __global__ void __launch_bounds__(256) maxpool3s2_quad_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out,
-                                                              long long quads, int H, int W, int OH, int OW,
-                                                              float* __restrict__ operand, OperandQuant oq)
+                                                              long long quads, int H, int W, int OH, int OW)
 {
     const int qw = OW / 4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < quads;
@@ -120,10 +100,6 @@ __global__ void __launch_bounds__(256) maxpool3s2_quad_kernel(const int32_t* __r
             best.w = max(best.w, max(b.y, max(b.z, b.w)));
         }
         *reinterpret_cast<int4*>(out + (bc * OH + oh) * OW + 4 * q) = best;
-        if (operand)
-            *reinterpret_cast<float4*>(operand + (bc * OH + oh) * OW + 4 * q) =
-                make_float4(operand_of_code(best.x, oq), operand_of_code(best.y, oq), operand_of_code(best.z, oq),
-                            operand_of_code(best.w, oq));
     }
 }
 
@@ -251,43 +227,9 @@ extern "C" int ds_quantize_f32(const float* x, int32_t* out, long long n, int ki
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
-extern "C" int ds_quantize_operand_f32(const float* x, float* out, long long n, int I, int F, void* stream)
-{
-    if (n < 0 || (n > 0 && (!x || !out))) return DS_ERR_BAD_ARG;
-    if (I < 1 || F < 0 || F > 16 || (I == 1 ? F + 2 : I + F) > 18) return DS_ERR_BAD_ARG;
-    if (n == 0) return DS_OK;
-    Quant q;
-    q.scale = float(1ll << F);
-    q.sign_mode = (I == 1);
-    q.lo = -float(1ll << (I - 1 + F));
-    q.hi = float(((1ll << (I - 1)) - 1) * (1ll << F));
-    const int threads = 256;
-    const long long want = (n + threads - 1) / threads;
-    const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
-    quantize_operand_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, n, q);
-    note_launch();
-    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
-}
-
 extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, int H, int W, int k, int stride,
                                 int pad, void* stream)
 {
-    return ds_maxpool2d_i32_operand(x, out, nullptr, B, C, H, W, k, stride, pad, 2, 0, stream);
-}
-
-extern "C" int ds_maxpool2d_i32_operand(const int32_t* x, int32_t* out, float* operand, int B, int C, int H, int W,
-                                        int k, int stride, int pad, int I, int F, void* stream)
-{
-    OperandQuant oq = {0, 0, 1, 0};
-    if (operand) {
-        if (I < 1 || F < 0 || F > 16 || (I == 1 ? F + 2 : I + F) > 18) return DS_ERR_BAD_ARG;
-        if (I == 1) {
-            oq.lo = -1; oq.hi = 1; oq.mul = 1 << F; oq.add = -(1 << F);
-        } else {
-            oq.lo = -(1 << (I - 1 + F));
-            oq.hi = ((1 << (I - 1)) - 1) * (1 << F);
-        }
-    }
     if (!x || !out || B < 0 || C <= 0 || H <= 0 || W <= 0 || k <= 0 || stride <= 0 || pad < 0 || 2 * pad > k)
         return DS_ERR_BAD_ARG;
     if (H + 2 * pad < k || W + 2 * pad < k) return DS_ERR_BAD_ARG;
@@ -296,19 +238,19 @@ extern "C" int ds_maxpool2d_i32_operand(const int32_t* x, int32_t* out, float* o
     if (total == 0) return DS_OK;
     const int threads = 256;
     if (k == 3 && stride == 2 && pad == 1 && W % 8 == 0 &&
-        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(operand)) & 15u) == 0) {
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0) {
         const long long quads = total / 4;  // OW = W / 2 is a multiple of 4
         const long long wantq = (quads + threads - 1) / threads;
         const int blocksq = int(wantq > 148 * 64 ? 148 * 64 : wantq);
         maxpool3s2_quad_kernel<<<blocksq, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, quads, H, W, OH,
-                                                                                          OW, operand, oq);
+                                                                                          OW);
         note_launch();
         return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
     }
     const long long want = (total + threads - 1) / threads;
     const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
     maxpool_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, total, H, W, OH, OW, k,
-                                                                            stride, pad, operand, oq);
+                                                                            stride, pad);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }

@@ -89,7 +89,7 @@ def last_kernel_error():
 
 
 def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=False, requant=False,
-          residual=None, act_bits=0, round_f32=False, workspace=None, operand_out=None):
+          residual=None, act_bits=0, round_f32=False, workspace=None):
     f = _ffi.Fuse()
     f.in_kind, f.out_kind = in_kind, out_kind
     f.act_integer_bits, f.act_fraction_bits = int(act_integer_bits), int(act_fraction_bits)
@@ -100,8 +100,6 @@ def _fuse(in_kind=0, out_kind=0, act_integer_bits=0, act_fraction_bits=0, relu=F
     if workspace is not None:
         f.workspace = workspace.data_ptr()
         f.workspace_bytes = workspace.numel() * workspace.element_size()
-    if operand_out is not None:
-        f.operand_out = operand_out.data_ptr()
     return f
 
 
@@ -235,7 +233,7 @@ def _prepared_weights(conc_weight, geometry, fuse, device):
 
 def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0, *, in_kind=_ffi.IN_I32,
                  out_kind=_ffi.OUT_I32, act_integer_bits=16, act_fraction_bits=16, relu=False, requant=False,
-                 residual=None, act_bits=0, round_f32=False, out=None, operand_out=None):
+                 residual=None, act_bits=0, round_f32=False, out=None):
     _check_tensor(input, "input", torch.int32 if in_kind in (_ffi.IN_I32, _ffi.IN_I32_CLAMP) else torch.float32)
     sh, sw = _pair(stride)
     ph, pw = _pair(padding)
@@ -251,12 +249,8 @@ def conv2d_fused(input, weight_shape, bias_i32, conc_weight, stride=1, padding=0
         _check_tensor(residual, "residual", torch.int32)
         if residual.shape != out.shape:
             raise RuntimeError("residual shape %s != output shape %s" % (tuple(residual.shape), tuple(out.shape)))
-    if operand_out is not None:
-        _check_tensor(operand_out, "operand_out", torch.float32)
-        if operand_out.shape != out.shape:
-            raise RuntimeError("operand_out shape %s != output shape %s" % (tuple(operand_out.shape), tuple(out.shape)))
     f = _fuse(in_kind, out_kind, act_integer_bits, act_fraction_bits, relu, requant, residual, act_bits, round_f32,
-              workspace(input.device), operand_out)
+              workspace(input.device))
     geometry = (B, C, H, W, OC, KH, KW, sh, sw, ph, pw)
     with torch.cuda.device(input.device):
         prepared = _prepared_weights(conc_weight, geometry, f, input.device)

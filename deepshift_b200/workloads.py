@@ -308,18 +308,11 @@ class IntPipeline(_Pipeline):
     logits.  Activations between layers are int32 codes (value * 2^F).  Every convolution reads
     them with the clamp of the consuming layer's quantiser (DS_IN_I32_CLAMP) and writes
     relu(acc + bias [+ residual]) rounded as the reference's fp32 tensor would hold it.
-
-    ``fp32_operands=True`` makes every layer that feeds a convolution also write clamp(v) + 0.5 as
-    fp32 (``ds_fuse_t.operand_out``), which the next convolution's staging code copies without
-    converting (``DS_IN_OPERAND_F32``).  Same results; measured on ResNet-18 at batch 256 it is no
-    faster (22.83 against 22.81 ms per step): the staging warps' instruction count is not what
-    limits the kernel.  Off by default.
     """
 
-    def __init__(self, net, weights, batch, device='cuda', use_graph=True, fp32_operands=False):
+    def __init__(self, net, weights, batch, device='cuda', use_graph=True):
         self.net, self.batch, self.device = net, batch, torch.device(device)
         self.I, self.F = net.act_integer_bits, net.act_fraction_bits
-        self.fp32_operands = fp32_operands
         self.packed, self.bias = [], []
         for L, w in zip(net.layers, weights):
             self.packed.append(utils.compress_bits(w['shift'].float(), w['sign'].float(), device=self.device))
@@ -340,22 +333,7 @@ class IntPipeline(_Pipeline):
         self.calls = []
         n_shift = sum(1 for s in net.steps if s[0] in ('conv', 'linear'))
         seen = 0
-        # Which step outputs are read by a convolution: those are also written as the fp32 operand
-        # (clamped code + 0.5) the convolution's staging code reads without converting anything.
-        use_operand = self.fp32_operands and utils.code_bits(self.I, self.F) <= 18
-        producer, feeds_conv = {'x': -1}, set()
-        for si, st in enumerate(net.steps):
-            if st[0] == 'conv':
-                feeds_conv.add(producer[st[2].get('src', 'x')])
-                producer[st[2].get('dst', 'x')] = si
-            elif st[0] == 'copy':
-                producer[st[2]] = producer[st[1]]
-            elif st[0] == 'shortcutA':
-                producer[st[2]] = si
-            elif st[0] in ('maxpool', 'gap', 'linear', 'flatten'):
-                producer['x'] = si
-        operand = {}   # tensor name -> fp32 operand tensor of the same shape
-        for si, st in enumerate(net.steps):
+        for st in net.steps:
             op = st[0]
             if op in ('conv', 'linear'):
                 seen += 1
@@ -366,20 +344,13 @@ class IntPipeline(_Pipeline):
                 xin = t[src]
                 in_fp32 = fp32[src]
                 if op == 'conv':
-                    in_kind = _ffi.IN_F32_CONV if in_fp32 else _ffi.IN_I32_CLAMP
                     if in_fp32 and L.k * L.k >= 25:
                         # a large window reads every input value many times: quantise it once in a
                         # pass of its own instead of inside the convolution's staging code
-                        if use_operand:
-                            xq = torch.empty(xin.shape, dtype=torch.float32, device=dev)
-                            self.calls.append(('quant_operand', xin, xq))
-                            xin, in_kind = xq, _ffi.IN_OPERAND_F32
-                        else:
-                            xq = torch.empty(xin.shape, dtype=torch.int32, device=dev)
-                            self.calls.append(('quant', xin, xq))
-                            xin, in_kind = xq, _ffi.IN_I32_CLAMP
-                    elif not in_fp32 and operand.get(src) is not None:
-                        xin, in_kind = operand[src], _ffi.IN_OPERAND_F32
+                        xq = torch.empty(xin.shape, dtype=torch.int32, device=dev)
+                        self.calls.append(('quant', xin, xq))
+                        xin, in_fp32 = xq, False
+                    in_kind = _ffi.IN_F32_CONV if in_fp32 else _ffi.IN_I32_CLAMP
                     B, C, H, W = xin.shape
                     OH, OW = (H + 2 * L.pad - L.k) // L.stride + 1, (W + 2 * L.pad - L.k) // L.stride + 1
                     out = torch.empty((B, L.cout, OH, OW), device=dev,
@@ -390,15 +361,12 @@ class IntPipeline(_Pipeline):
                     out = torch.empty((xin.shape[0], L.cout), device=dev,
                                       dtype=torch.float32 if lastlayer else torch.int32)
                 res = t[o['add']] if o.get('add') else None
-                opnd = None
-                if op == 'conv' and use_operand and not lastlayer and si in feeds_conv:
-                    opnd = torch.empty(out.shape, dtype=torch.float32, device=dev)
                 fuse = kernels._fuse(in_kind, _ffi.OUT_F32 if lastlayer else _ffi.OUT_I32, self.I, self.F,
                                      relu=bool(o.get('relu')), requant=False, residual=res,
-                                     round_f32=not lastlayer, workspace=self.workspace, operand_out=opnd)
-                self.calls.append((op, xin, li, L, out, fuse, res, opnd))
+                                     round_f32=not lastlayer, workspace=self.workspace)
+                self.calls.append((op, xin, li, L, out, fuse, res))
                 dst = o.get('dst', 'x')
-                t[dst], fp32[dst], operand[dst] = out, lastlayer, opnd
+                t[dst], fp32[dst] = out, lastlayer
             elif op == 'maxpool':
                 _, k, s_, p_ = st
                 xin = t['x']
@@ -406,25 +374,24 @@ class IntPipeline(_Pipeline):
                 B, C, H, W = xin.shape
                 out = torch.empty((B, C, (H + 2 * p_ - k) // s_ + 1, (W + 2 * p_ - k) // s_ + 1),
                                   dtype=torch.int32, device=dev)
-                opnd = torch.empty(out.shape, dtype=torch.float32, device=dev) if (use_operand and si in feeds_conv) else None
-                self.calls.append(('maxpool', xin, k, s_, p_, out, opnd))
-                t['x'], operand['x'] = out, opnd
+                self.calls.append(('maxpool', xin, k, s_, p_, out))
+                t['x'] = out
             elif op == 'gap':
                 xin = t['x']
                 out = torch.empty((xin.shape[0], xin.shape[1]), dtype=torch.int32, device=dev)
                 self.calls.append(('gap', xin, out))
-                t['x'], operand['x'] = out, None
+                t['x'] = out
             elif op == 'flatten':
                 t['x'] = t['x'].reshape(t['x'].shape[0], -1)
             elif op == 'copy':
-                t[st[2]], fp32[st[2]], operand[st[2]] = t[st[1]], fp32[st[1]], operand.get(st[1])
+                t[st[2]], fp32[st[2]] = t[st[1]], fp32[st[1]]
             elif op == 'shortcutA':
                 xin = t[st[1]]
                 pad = st[3] // 4
                 B, C, H, W = xin.shape
                 out = torch.zeros((B, C + 2 * pad, (H + 1) // 2, (W + 1) // 2), dtype=torch.int32, device=dev)
                 self.calls.append(('shortcutA', xin, out, pad))
-                t[st[2]], fp32[st[2]], operand[st[2]] = out, False, None
+                t[st[2]], fp32[st[2]] = out, False
         self.out = t['x']
 
     def _launch_all(self):
@@ -433,7 +400,7 @@ class IntPipeline(_Pipeline):
         for c in self.calls:
             op = c[0]
             if op == 'conv':
-                _, xin, li, L, out, fuse, _res, _opnd = c
+                _, xin, li, L, out, fuse, _res = c
                 B, C, H, W = xin.shape
                 cw = self.packed[li]
                 if fuse.prepared is None and fuse.prepared_bytes == 0:
@@ -449,7 +416,7 @@ class IntPipeline(_Pipeline):
                                       cw.base, fuse, stream)
                 _ffi.check(rc, "conv2d_ex")
             elif op == 'linear':
-                _, xin, li, L, out, fuse, _res, _opnd = c
+                _, xin, li, L, out, fuse, _res = c
                 cw = self.packed[li]
                 rc = lib.ds_linear_ex(xin.data_ptr(), cw.data.data_ptr(), self.bias[li].data_ptr(), out.data_ptr(),
                                       xin.shape[0], xin.shape[1], L.cout, cw.bits, cw.base, fuse, stream)
@@ -458,16 +425,11 @@ class IntPipeline(_Pipeline):
                 _, xin, xq = c
                 _ffi.check(lib.ds_quantize_f32(xin.data_ptr(), xq.data_ptr(), xin.numel(), _ffi.IN_F32_CONV, self.I,
                                                self.F, stream), "quantize_f32")
-            elif op == 'quant_operand':
-                _, xin, xq = c
-                _ffi.check(lib.ds_quantize_operand_f32(xin.data_ptr(), xq.data_ptr(), xin.numel(), self.I, self.F,
-                                                       stream), "quantize_operand_f32")
             elif op == 'maxpool':
-                _, xin, k, s_, p_, out, opnd = c
+                _, xin, k, s_, p_, out = c
                 B, C, H, W = xin.shape
-                _ffi.check(lib.ds_maxpool2d_i32_operand(xin.data_ptr(), out.data_ptr(),
-                                                        opnd.data_ptr() if opnd is not None else None, B, C, H, W,
-                                                        k, s_, p_, self.I, self.F, stream), "maxpool2d_i32")
+                _ffi.check(lib.ds_maxpool2d_i32(xin.data_ptr(), out.data_ptr(), B, C, H, W, k, s_, p_, stream),
+                           "maxpool2d_i32")
             elif op == 'gap':
                 _, xin, out = c
                 B, C, H, W = xin.shape

@@ -55,16 +55,12 @@ enum {
     DS_IN_I32 = 0,       /* int32 fixed point (what the reference kernels receive)                         */
     DS_IN_F32_CONV = 1,  /* fp32, quantised in the kernel as Conv2dShift does: clamp(floor(x*2^F)) -- utils.py:7-21, modules.py:153,317 */
     DS_IN_F32_LINEAR = 2,/* fp32, quantised as LinearShift does: trunc(x*2^F), no clamp -- modules.py:25 */
-    DS_IN_I32_CLAMP = 3, /* int32 fixed point, clamped on read to [-2^(I-1+F), (2^(I-1)-1)*2^F]: what
+    DS_IN_I32_CLAMP = 3  /* int32 fixed point, clamped on read to [-2^(I-1+F), (2^(I-1)-1)*2^F]: what
                             Conv2dShift's round_to_fixed does to a value already on the 2^-F grid.
                             Lets one unclamped tensor feed both a convolution and a residual add.
                             With I == 1 round_to_fixed is sign(x) - 1 (utils.py:12-13), so a code
                             c < 0, c == 0, c > 0 is read as -2^(F+1), -2^F, 0: apply it to codes that
                             have NOT been through round_to_fixed yet (it is not idempotent there). */
-    DS_IN_OPERAND_F32 = 4 /* fp32 holding code + 0.5, the code already clamped by this layer's quantiser:
-                            what ds_fuse_t.operand_out of the producing layer (or ds_quantize_operand_f32)
-                            wrote.  The kernel stages it without any conversion.  FP32-pipe path only
-                            (base == 0, I + F <= 18).  */
 };
 
 /* Output element kinds of the *_ex entry points. */
@@ -123,11 +119,6 @@ typedef struct {
                                weight expansion (two small kernels).  NULL = expand per launch (with
                                a workspace) or decode in the kernel (without).                     */
     long long prepared_bytes;
-    float *operand_out;     /* optional second output, same shape and layout as the int32 output: the value
-                               the NEXT layer's staging code wants, clamp(v) + 0.5 as fp32 with the clamp of
-                               act_integer_bits / act_fraction_bits (round_to_fixed on a value already on the
-                               grid).  A layer that reads it passes in_kind = DS_IN_OPERAND_F32.  Needs
-                               out_kind = DS_OUT_I32 and 16-byte alignment.  NULL = not written.     */
 } ds_fuse_t;
 
 /*
@@ -202,11 +193,6 @@ int ds_compress(const int32_t *shiftp, const int32_t *sign, int32_t *packed, int
 int ds_quantize_f32(const float *x, int32_t *out, long long n, int kind, int act_integer_bits,
                     int act_fraction_bits, void *stream);
 
-/* The same quantiser (DS_IN_F32_CONV rule) writing the fp32 operand code + 0.5 that
- * DS_IN_OPERAND_F32 reads; I + F <= 18. */
-int ds_quantize_operand_f32(const float *x, float *out, long long n, int act_integer_bits,
-                            int act_fraction_bits, void *stream);
-
 /*
  * Inter-layer glue of the integer pipeline (no counterpart in the reference's native code, which
  * leaves these steps to torch ops on fp32: F.max_pool2d / adaptive_avg_pool2d in the model
@@ -218,10 +204,6 @@ int ds_quantize_operand_f32(const float *x, float *out, long long n, int act_int
  */
 int ds_maxpool2d_i32(const int32_t *x, int32_t *out, int B, int C, int H, int W, int k, int stride,
                      int pad, void *stream);
-/* ds_maxpool2d_i32 that also writes the fp32 operand (clamp of I, F, + 0.5) of the pooled codes. */
-int ds_maxpool2d_i32_operand(const int32_t *x, int32_t *out, float *operand_out, int B, int C, int H, int W,
-                             int k, int stride, int pad, int act_integer_bits, int act_fraction_bits,
-                             void *stream);
 int ds_avgpool_fix_i32(const int32_t *x, int32_t *out, int B, int C, int H, int W, int F, void *stream);
 
 /*
@@ -348,7 +330,7 @@ int ds_last_kernel_error(int *flag);
  * packed weights and residual and of every global store in the linear / convolution kernels against
  * the extents implied by the call's arguments.  An access outside is skipped, never performed, and
  * the first one leaves its kind in a status word: 1 activations, 2 packed weights, 3 output /
- * residual / operand_out.  Nothing traps.  (The TMA-fed staged kernel is not instrumented: the
+ * residual.  Nothing traps.  (The TMA-fed staged kernel is not instrumented: the
  * tensor map bounds its loads in hardware.)
  *   ds_bounds_status        reads and clears the status word (synchronises the device); *checked
  *                           says whether this library was built with the checks.

@@ -849,36 +849,6 @@ def test_ps_module_repacks_when_parameters_change(oracle, cuda_device):
     assert not torch.equal(lin(xl), y0)
 
 
-@pytest.mark.parametrize("shape", [(3, 16, 28, 28, 40, 3, 1, 1),    # four-pixel staging
-                                   (3, 24, 14, 14, 130, 3, 1, 1),   # two-pixel staging
-                                   (2, 3, 32, 32, 64, 7, 2, 3),     # the stem's staging
-                                   (4, 20, 7, 9, 70, 3, 1, 1),      # plain rows
-                                   (3, 12, 10, 10, 33, 1, 2, 0),    # 1x1 stride 2
-                                   (2, 6, 11, 11, 20, 5, 1, 2)])    # table-free 5x5
-def test_conv_reads_and_writes_fp32_operands(oracle, cuda_device, shape):
-    """DS_IN_OPERAND_F32 / operand_out: a layer hands the next one clamp(v) + 0.5 as fp32, which the
-    staging code of every access mode copies without converting; results equal the int32 path."""
-    from deepshift_b200 import _ffi, kernels
-    B, C, H, W, OC, k, s, p = shape
-    rng = np.random.default_rng(sum(shape))
-    x = (acts_q16(rng, (B, C, H, W)) * 3).astype(np.int32)          # beyond the clamp
-    xc = np.clip(x, -32768, 28672)
-    shift, sign = weights(rng, (OC, C, k, k))
-    bias = rng.integers(-2000, 2000, OC).astype(np.int32)
-    ref = oracle.conv2d(xc, shift, sign, bias, (s, s), (p, p))
-    ref = np.maximum(ref, 0)
-    cw = _cw(shift, sign, cuda_device)
-    opnd_in = _t((xc.astype(np.float32) + 0.5), cuda_device)
-    opnd_out = torch.full(ref.shape, -7.0, dtype=torch.float32, device=cuda_device)
-    out = kernels.conv2d_fused(opnd_in, (OC, C, k, k), _t(bias, cuda_device), cw, s, p, in_kind=_ffi.IN_OPERAND_F32,
-                               act_integer_bits=4, act_fraction_bits=12, relu=True, operand_out=opnd_out)
-    assert np.array_equal(out.cpu().numpy(), ref)
-    assert np.array_equal(opnd_out.cpu().numpy(), np.clip(ref, -32768, 28672).astype(np.float32) + 0.5)
-    with pytest.raises(RuntimeError):   # the operand form exists for the FP32-pipe path only
-        kernels.conv2d_fused(opnd_in, (OC, C, k, k), _t(bias, cuda_device), cw, s, p, in_kind=_ffi.IN_OPERAND_F32,
-                             act_integer_bits=16, act_fraction_bits=16)
-
-
 @pytest.mark.parametrize("M", [1, 3, 8, 16, 23, 64])
 def test_small_batch_linear_with_fused_epilogue(oracle, cuda_device, M):
     """Small batches (the kernels that split K across lanes / across CTAs) with everything fused:

@@ -26,8 +26,6 @@ def test_networks_bit_exact_against_oracle(oracle, cuda_device, name, batch, kw)
     for graph in (False, True):
         pipe = W.IntPipeline(net, ws, batch, cuda_device, use_graph=graph)
         assert np.array_equal(pipe.run(x.to(cuda_device)).cpu().numpy(), ref), graph
-    pipe = W.IntPipeline(net, ws, batch, cuda_device, use_graph=False, fp32_operands=True)
-    assert np.array_equal(pipe.run(x.to(cuda_device)).cpu().numpy(), ref)
 
 
 def test_resnet18_full_resolution_sample_against_oracle(oracle, cuda_device):
