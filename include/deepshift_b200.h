@@ -167,7 +167,9 @@ int ds_conv2d_ex(const void *x, const int32_t *packed, const int32_t *bias, void
  * cudaMalloc / cudaFree and call no allocating library routine.
  *   - Limit: at most 16384 output tiles per call, a tile being 256 output positions (b,oh,ow) by
  *     128 output channels (64 when OC <= 64).  Larger problems return DS_ERR_SCRATCH and run nothing;
- *     use ds_conv2d_ex with a workspace, or without one, for those.
+ *     use ds_conv2d_ex with a workspace, or without one, for those.  The limit is applied by tile
+ *     count alone, also to calls whose launch would not have used a counter (integer path, few
+ *     output channels).
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current).  Make that first call before starting any stream capture.
  *   - All calls on a device share the array.  Every call clears the counters it will use on
