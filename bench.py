@@ -610,12 +610,19 @@ def main():
         local = int(os.environ.get("LOCAL_RANK", "0"))
     try:
         run_ours(args, rank, world, local)
-    finally:
+    except BaseException:
         if world > 1:
-            import torch.distributed as dist
-            if dist.is_initialized():
-                dist.barrier()
-                dist.destroy_process_group()
+            # leave at once: the other ranks must not be kept waiting in a collective for this one
+            import traceback
+            traceback.print_exc()
+            sys.stderr.flush()
+            os._exit(1)
+        raise
+    if world > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -69,6 +69,18 @@ def build(force=False, verbose=False, extra_flags=(), checked=False):
         extra_flags = tuple(extra_flags) + CHECKED_FLAGS
     if not force and is_current(checked):
         return lib_path
+    # One builder at a time: the ranks of a multi-process job may all find the library stale at
+    # once.  The others wait here and then find it current.
+    import fcntl
+    os.makedirs(LIB_DIR, exist_ok=True)
+    with open(os.path.join(LIB_DIR, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current(checked):
+            return lib_path
+        return _build_locked(force, verbose, extra_flags, checked, lib_path, stamp)
+
+
+def _build_locked(force, verbose, extra_flags, checked, lib_path, stamp):
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found and %s is missing or stale" % lib_path)

@@ -22,9 +22,11 @@ def shard_bounds(total, world_size, rank):
     return begin, begin + base + (1 if rank < rem else 0)
 
 
-def init_from_env(backend=None):
+def init_from_env(backend=None, timeout_s=180):
     """Joins the process group described by RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT (as
-    torchrun sets them).  Returns (rank, world_size, local_rank); a single process needs no group."""
+    torchrun sets them).  Returns (rank, world_size, local_rank); a single process needs no group.
+    ``timeout_s``: how long a collective waits for a rank that never arrives before it fails (the
+    default of the backends is ten minutes; inference steps take milliseconds)."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
@@ -35,7 +37,9 @@ def init_from_env(backend=None):
             backend = "nccl" if torch.cuda.is_available() else "gloo"
         if backend == "nccl":
             torch.cuda.set_device(local)
-        dist.init_process_group(backend=backend, rank=rank, world_size=world)
+        import datetime
+        dist.init_process_group(backend=backend, rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=timeout_s))
     return rank, world, local
 
 
