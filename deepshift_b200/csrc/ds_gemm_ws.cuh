@@ -11,8 +11,9 @@
 //     and decode them through the lookup table, one k-tile ahead of the consumers.  For a
 //     linear layer (x is [M,K]) a producer thread owns one row and reads its k-tile with
 //     16-byte loads; its stores into the k-major stage are conflict-free.
-//   * The two groups meet only at mbarriers: full[s] (one arrival per producer warp) and empty[s]
-//     (one per consumer warp) for each of the two stages.  Global-load latency, the decode chains
+//   * The two groups meet only at mbarriers: full[s] (one arrival per producer warp, plus one per
+//     producer thread when its asynchronous weight copies land) and empty[s] (one per consumer
+//     warp) for each of the two stages.  Global-load latency, the decode chains
 //     and the stores of a stage all overlap the FFMA stream of the previous stage, so the
 //     FMA pipe no longer idles while "everybody stages".
 //
@@ -120,9 +121,11 @@ __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
 }
 
-__device__ __forceinline__ void cp_async_wait_all()
+// One arrival on `bar` once every cp.async this thread has issued so far has landed.  The thread
+// does not wait; the barrier's expected count must include this arrival (.noinc).
+__device__ __forceinline__ void cp_async_arrive_on(unsigned long long* bar)
 {
-    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 2, %0;" ::"n"(WS_CONS) : "memory"); }
@@ -196,7 +199,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     for (int i = t; i < 4 * BN; i += WS_NT) (&s.negc[0][0])[i] = 0;
     if (t == 0) {
         for (int i = 0; i < WS_STAGES; ++i) {
-            mbar_init(&s.full[i], WS_PROD / 32);   // one arrival per warp
+            // one arrival per producer warp (x stored) and, with expanded weights, one per producer
+            // thread when its asynchronous weight copies have landed
+            mbar_init(&s.full[i], WS_PROD / 32 + (PRE ? WS_PROD : 0));
             mbar_init(&s.empty[i], WS_CONS / 32);
         }
         s.err = 0;
@@ -587,14 +592,15 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                 const int k0 = tile * p.bk;
                 // Expanded weights are 0 beyond K, so the x values stored there need no care.
                 const bool last = !PRE && tile + 1 >= p.ntiles;
-                if (PRE) copy_w_async(tile, st, cur.n0);
+                if (PRE) {
+                    copy_w_async(tile, st, cur.n0);
+                    cp_async_arrive_on(&s.full[st]);  // nobody waits here for the copies
+                }
                 with_input_kind(p, [&](auto ink_tag) {
                     if (last) store_x(ink_tag, std::true_type(), st, k0);
                     else store_x(ink_tag, std::false_type(), st, k0);
                 });
-                if (PRE) {
-                    cp_async_wait_all();
-                } else {
+                if (!PRE) {
                     int* negc = s.negc[seq & 3];
                     switch (p.dec.num) {
                         case 4: store_w(std::integral_constant<int, 4>(), st, negc); break;
