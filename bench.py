@@ -269,7 +269,9 @@ def run_ours(args, rank, world, local):
     value = world * B * args.steps / (ms_total * 1e-3)
 
     # ---- end to end through the drop-in modules, host buffers, copies inside the timed region
-    model = W.ModuleNet(net, ws, dev).eval()
+    # (the ReLUs and residual additions that follow a shift layer go to its forward as fusion hints)
+    model = W.ModuleNet(net, ws, dev, fuse=True).eval()
+    model_plain = W.ModuleNet(net, ws, dev, fuse=False).eval()
     y_host = torch.empty((B, net.layers[-1].cout), dtype=torch.float32).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
 
@@ -279,7 +281,7 @@ def run_ours(args, rank, world, local):
     x_bufs = [torch.empty_like(x_dev) for _ in range(2)]
     y_hosts = [torch.empty_like(y_host).pin_memory() for _ in range(2)]
 
-    def e2e_run(nsteps):
+    def e2e_run(nsteps, model=model):
         main = torch.cuda.current_stream(dev)
         copied = [torch.cuda.Event() for _ in range(nsteps)]
         consumed = [torch.cuda.Event() for _ in range(nsteps)]
@@ -315,6 +317,20 @@ def run_ours(args, rank, world, local):
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         e2e_ms = float(tmax.item())
     e2e_value = world * B * e2e_steps / (e2e_ms * 1e-3)
+    # the same without the hints (every ReLU and residual addition a torch kernel of its own)
+    e2e_run(2, model_plain)
+    barrier()
+    e0.record()
+    e2e_run(e2e_steps, model_plain)
+    e1.record()
+    barrier()
+    plain_ms = e0.elapsed_time(e1)
+    if world > 1:
+        tmax = torch.tensor([plain_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        plain_ms = float(tmax.item())
+    e2e_plain = world * B * e2e_steps / (plain_ms * 1e-3)
+    del model_plain
     clocks = sampler.stop()
 
     if kernels.last_kernel_error():
@@ -408,8 +424,9 @@ def run_ours(args, rank, world, local):
         "roofline": roofline,
         "cpu_baseline": ({"value": cpu_val, "unit": UNIT, **cpu_info} if cpu_info else None),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": y_host.numel() * 4,
-                "api": "ModuleNet of LinearShift/Conv2dShift(use_kernel=True), pinned host input -> host logits",
-                "steps": e2e_steps},
+                "api": "ModuleNet of LinearShift/Conv2dShift(use_kernel=True), pinned host input -> host logits; "
+                       "ReLU / residual add after a shift layer passed to its forward as fusion hints",
+                "without_fusion_hints": e2e_plain, "steps": e2e_steps},
         "parity": parity,
         "sweep": sweep,
         "gpu_launches": args.steps * pipe.n_launches,

@@ -255,6 +255,45 @@ extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, in
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
+// y = relu?(y + r) in place, four elements per thread where the pointers allow.
+__global__ void __launch_bounds__(256) add_relu_f32_kernel(float* __restrict__ y, const float* r, long long n,
+                                                           int relu, int vec)
+{
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    auto fin = [&](float a, float b) {
+        const float f = a + b;
+        return (relu && f < 0.f) ? 0.f : f;
+    };
+    if (vec) {
+        const long long n4 = n >> 2;
+        float4* y4 = reinterpret_cast<float4*>(y);
+        const float4* r4 = reinterpret_cast<const float4*>(r);
+        for (long long i = first; i < n4; i += stride) {
+            const float4 a = y4[i];
+            const float4 b = r ? __ldg(r4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            y4[i] = make_float4(fin(a.x, b.x), fin(a.y, b.y), fin(a.z, b.z), fin(a.w, b.w));
+        }
+        for (long long i = (n4 << 2) + first; i < n; i += stride) y[i] = fin(y[i], r ? r[i] : 0.f);
+    } else {
+        for (long long i = first; i < n; i += stride) y[i] = fin(y[i], r ? r[i] : 0.f);
+    }
+}
+
+extern "C" int ds_add_relu_f32(float* y, const float* r, long long n, int relu, void* stream)
+{
+    if (!y || n < 0) return DS_ERR_BAD_ARG;
+    if (n == 0 || (!r && !relu)) return DS_OK;
+    if ((reinterpret_cast<uintptr_t>(y) & 3u) || (reinterpret_cast<uintptr_t>(r) & 3u)) return DS_ERR_ALIGN;
+    const int vec = ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(r)) & 15u) == 0;
+    const int threads = 256;
+    const long long want = ((vec ? (n + 3) / 4 : n) + threads - 1) / threads;
+    const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
+    add_relu_f32_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(y, r, n, relu, vec);
+    note_launch();
+    return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
 extern "C" int ds_avgpool_fix_i32(const int32_t* x, int32_t* out, int B, int C, int H, int W, int F, void* stream)
 {
     if (!x || !out || B < 0 || C <= 0 || H <= 0 || W <= 0 || F < 0 || F > 30) return DS_ERR_BAD_ARG;

@@ -293,6 +293,21 @@ def maxpool2d_i32(input, kernel_size, stride, padding=0, out=None):
     return out
 
 
+def add_relu_f32_(y, residual=None, relu=False):
+    """In place, one pass: ``y += residual`` (when given), then ``y = relu(y)`` (when asked) -- the
+    fp32 glue after a shift layer in a residual block, bit-identical to the two torch ops."""
+    _check_tensor(y, "y", torch.float32)
+    if residual is not None:
+        _check_tensor(residual, "residual", torch.float32)
+        if residual.shape != y.shape:
+            raise RuntimeError("residual shape %s != output shape %s" % (tuple(residual.shape), tuple(y.shape)))
+    with torch.cuda.device(y.device):
+        rc = _ffi.lib().ds_add_relu_f32(y.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                        y.numel(), int(bool(relu)), _stream_ptr(y.device))
+    _ffi.check(rc, "add_relu_f32_")
+    return y
+
+
 def avgpool_fix_i32(input, act_fraction_bits, out=None):
     """Global average pooling of int32 activations followed by the LinearShift entry conversion;
     returns int32 [B, C]."""

@@ -110,17 +110,28 @@ class LinearShift(_ShiftBase):
             bound = 1 / math.sqrt(fan_in)
             init.uniform_(self.bias, -bound, bound)
 
-    def forward(self, input):
+    def forward(self, input, residual=None, relu=False):
+        """``residual`` and ``relu`` are optional fusion hints (no counterpart in the reference, whose
+        forward takes the input only): the result equals ``F.relu(self(input) + residual)`` (each part
+        only when given) bit for bit.  With ``use_kernel=True`` a ReLU alone happens in the layer's
+        epilogue; with a residual, addition and ReLU are one in-place pass over the output instead of
+        two torch kernels."""
         if self.use_kernel:
             _kernel_mode_check(self)
             x = input.reshape(-1, self.in_features).float().contiguous()
             out = kernels.linear_fused(x, self.out_features, self._bias_fixed(like_conv=False),
                                        self._packed(x.device), in_kind=_ffi.IN_F32_LINEAR,
                                        out_kind=_ffi.OUT_F32, act_integer_bits=self.act_integer_bits,
-                                       act_fraction_bits=self.act_fraction_bits)
+                                       act_fraction_bits=self.act_fraction_bits,
+                                       relu=relu and residual is None)
+            if residual is not None:
+                kernels.add_relu_f32_(out, residual.reshape(-1, self.out_features).float().contiguous(), relu)
             return out.reshape(*input.shape[:-1], self.out_features)
         self.shift.data = ste.clamp(self.shift.data, *self.shift_range)
-        return F.linear(input, self._float_weight(), self.bias)
+        out = F.linear(input, self._float_weight(), self.bias)
+        if residual is not None:
+            out = out + residual
+        return F.relu(out) if relu else out
 
     def extra_repr(self):
         return 'in_features={}, out_features={}, bias={}'.format(
@@ -204,7 +215,12 @@ class Conv2dShift(_ConvNdShift):
             bias, padding_mode, check_grad, freeze_sign, rounding, weight_bits, act_integer_bits,
             act_fraction_bits)
 
-    def forward(self, input):
+    def forward(self, input, residual=None, relu=False):
+        """``residual`` and ``relu`` are optional fusion hints (no counterpart in the reference, whose
+        forward takes the input only): the result equals ``F.relu(self(input) + residual)`` (each part
+        only when given) bit for bit.  With ``use_kernel=True`` a ReLU alone happens in the layer's
+        epilogue; with a residual, addition and ReLU are one in-place pass over the output instead of
+        two torch kernels."""
         if self.padding_mode == 'circular':
             # modules.py:323-331; padding fp32 before the quantiser equals padding after it.
             expanded_padding = ((self.padding[1] + 1) // 2, self.padding[1] // 2,
@@ -225,15 +241,22 @@ class Conv2dShift(_ConvNdShift):
                 # kernel gets them as plain int32 with their bound
                 x = kernels.quantize(x, self.act_integer_bits, self.act_fraction_bits, like_conv=True)
                 in_kind, act_bits = _ffi.IN_I32, utils.code_bits(self.act_integer_bits, self.act_fraction_bits)
-            return kernels.conv2d_fused(x, tuple(self.shift.shape), self._bias_fixed(like_conv=True),
-                                        self._packed(x.device), self.stride, padding,
-                                        in_kind=in_kind, out_kind=_ffi.OUT_F32,
-                                        act_integer_bits=self.act_integer_bits,
-                                        act_fraction_bits=self.act_fraction_bits, act_bits=act_bits)
+            out = kernels.conv2d_fused(x, tuple(self.shift.shape), self._bias_fixed(like_conv=True),
+                                       self._packed(x.device), self.stride, padding,
+                                       in_kind=in_kind, out_kind=_ffi.OUT_F32,
+                                       act_integer_bits=self.act_integer_bits,
+                                       act_fraction_bits=self.act_fraction_bits, act_bits=act_bits,
+                                       relu=relu and residual is None)
+            if residual is not None:
+                kernels.add_relu_f32_(out, residual.float().contiguous(), relu)
+            return out
         self.shift.data = ste.clamp(self.shift.data, *self.shift_range)
         input_fixed_point = ste.round_fixed_point(input, self.act_integer_bits, self.act_fraction_bits)
         bias_fixed_point = None
         if self.bias is not None:
             bias_fixed_point = ste.round_fixed_point(self.bias, self.act_integer_bits, self.act_fraction_bits)
-        return F.conv2d(input_fixed_point, self._float_weight(), bias_fixed_point, self.stride, padding,
-                        self.dilation, self.groups)
+        out = F.conv2d(input_fixed_point, self._float_weight(), bias_fixed_point, self.stride, padding,
+                       self.dilation, self.groups)
+        if residual is not None:
+            out = out + residual
+        return F.relu(out) if relu else out

@@ -102,21 +102,31 @@ class LinearShiftQ(_ShiftQBase):
             bound = 1 / math.sqrt(fan_in)
             init.uniform_(self.bias, -bound, bound)
 
-    def forward(self, input):
+    def forward(self, input, residual=None, relu=False):
+        """``residual`` and ``relu`` are optional fusion hints (no counterpart in the reference, whose
+        forward takes the input only): the result equals ``F.relu(self(input) + residual)`` (each part
+        only when given) bit for bit.  With ``use_kernel=True`` a ReLU alone happens in the layer's
+        epilogue; with a residual, addition and ReLU are one in-place pass over the output instead of
+        two torch kernels."""
         if self.use_kernel:
             self._check_kernel_mode()
             x = self._input_codes(input.reshape(-1, self.in_features))
             out = kernels.linear_fused(x, self.out_features, self._bias_fixed(), self._packed(x.device),
                                        in_kind=_ffi.IN_I32, out_kind=_ffi.OUT_F32,
                                        act_integer_bits=self.act_integer_bits,
-                                       act_fraction_bits=self.act_fraction_bits, act_bits=self._act_bits())
+                                       act_fraction_bits=self.act_fraction_bits, act_bits=self._act_bits(),
+                                       relu=relu and residual is None)
+            if residual is not None:
+                kernels.add_relu_f32_(out, residual.reshape(-1, self.out_features).float().contiguous(), relu)
             return out.reshape(*input.shape[:-1], self.out_features)
         weight_q = utils.round_power_of_2(self._clamped_weight(), self.rounding)
         input_fixed_point = utils.round_to_fixed(input, self.act_integer_bits, self.act_fraction_bits)
         out = input_fixed_point.mm(weight_q.t())
         if self.bias is not None:
             out += self.bias.unsqueeze(0).expand_as(out)  # unrounded, as modules_q.py:130
-        return out
+        if residual is not None:
+            out = out + residual
+        return F.relu(out) if relu else out
 
     def extra_repr(self):
         return 'in_features={}, out_features={}, bias={}'.format(
@@ -195,7 +205,12 @@ class Conv2dShiftQ(_ConvNdShiftQ):
             in_channels, out_channels, kernel_size, stride, padding, dilation, False, _pair(0), groups, bias,
             padding_mode, check_grad, rounding, weight_bits, act_integer_bits, act_fraction_bits)
 
-    def forward(self, input):
+    def forward(self, input, residual=None, relu=False):
+        """``residual`` and ``relu`` are optional fusion hints (no counterpart in the reference, whose
+        forward takes the input only): the result equals ``F.relu(self(input) + residual)`` (each part
+        only when given) bit for bit.  With ``use_kernel=True`` a ReLU alone happens in the layer's
+        epilogue; with a residual, addition and ReLU are one in-place pass over the output instead of
+        two torch kernels."""
         padding = self.padding
         if self.padding_mode == 'circular':  # modules_q.py:291-296
             expanded_padding = ((self.padding[1] + 1) // 2, self.padding[1] // 2,
@@ -212,14 +227,21 @@ class Conv2dShiftQ(_ConvNdShiftQ):
                 # a large window reads every input value many times: quantise once, in its own pass
                 x = self._input_codes(x)
                 in_kind, act_bits = _ffi.IN_I32, self._act_bits()
-            return kernels.conv2d_fused(x, tuple(self.weight.shape), self._bias_fixed(), self._packed(x.device),
-                                        self.stride, padding, in_kind=in_kind, out_kind=_ffi.OUT_F32,
-                                        act_integer_bits=self.act_integer_bits,
-                                        act_fraction_bits=self.act_fraction_bits, act_bits=act_bits)
+            out = kernels.conv2d_fused(x, tuple(self.weight.shape), self._bias_fixed(), self._packed(x.device),
+                                       self.stride, padding, in_kind=in_kind, out_kind=_ffi.OUT_F32,
+                                       act_integer_bits=self.act_integer_bits,
+                                       act_fraction_bits=self.act_fraction_bits, act_bits=act_bits,
+                                       relu=relu and residual is None)
+            if residual is not None:
+                kernels.add_relu_f32_(out, residual.float().contiguous(), relu)
+            return out
         weight_q = utils.round_power_of_2(self._clamped_weight(), self.rounding)
         input_fixed_point = utils.round_to_fixed(input, self.act_integer_bits, self.act_fraction_bits)
         bias_fixed_point = None
         if self.bias is not None:
             bias_fixed_point = utils.round_to_fixed(self.bias, self.act_integer_bits, self.act_fraction_bits)
-        return F.conv2d(input_fixed_point, weight_q, bias_fixed_point, self.stride, padding, self.dilation,
-                        self.groups)
+        out = F.conv2d(input_fixed_point, weight_q, bias_fixed_point, self.stride, padding, self.dilation,
+                       self.groups)
+        if residual is not None:
+            out = out + residual
+        return F.relu(out) if relu else out

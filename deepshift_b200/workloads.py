@@ -206,11 +206,13 @@ def _shortcut_a(x, planes):
 
 class ModuleNet(nn.Module):
     """The network as the reference would run it with ``use_kernel=True``: shift modules and fp32
-    glue."""
+    glue.  ``fuse=True`` hands the residual additions and ReLUs that follow a shift layer to that
+    layer's ``forward`` as fusion hints (same values, fewer passes over the activations)."""
 
-    def __init__(self, net, weights, device='cuda', use_kernel=True):
+    def __init__(self, net, weights, device='cuda', use_kernel=True, fuse=False):
         super().__init__()
         self.net = net
+        self.fuse = fuse
         mods = []
         kw = dict(use_kernel=use_kernel, use_cuda=True, rounding='deterministic', weight_bits=net.weight_bits,
                   act_integer_bits=net.act_integer_bits, act_fraction_bits=net.act_fraction_bits)
@@ -235,15 +237,22 @@ class ModuleNet(nn.Module):
             op = st[0]
             if op == 'conv':
                 li, o = st[1], st[2]
-                y = self.layers[li](t[o.get('src', 'x')])
-                if o.get('add'):
-                    y = y + t[o['add']]
-                if o.get('relu'):
-                    y = F.relu(y)
+                if self.fuse:
+                    y = self.layers[li](t[o.get('src', 'x')], residual=t[o['add']] if o.get('add') else None,
+                                        relu=bool(o.get('relu')))
+                else:
+                    y = self.layers[li](t[o.get('src', 'x')])
+                    if o.get('add'):
+                        y = y + t[o['add']]
+                    if o.get('relu'):
+                        y = F.relu(y)
                 t[o.get('dst', 'x')] = y
             elif op == 'linear':
-                y = self.layers[st[1]](t['x'])
-                t['x'] = F.relu(y) if st[2].get('relu') else y
+                if self.fuse:
+                    t['x'] = self.layers[st[1]](t['x'], relu=bool(st[2].get('relu')))
+                else:
+                    y = self.layers[st[1]](t['x'])
+                    t['x'] = F.relu(y) if st[2].get('relu') else y
             elif op == 'maxpool':
                 t['x'] = F.max_pool2d(t['x'], st[1], st[2], st[3])
             elif op == 'gap':

@@ -209,6 +209,14 @@ int ds_maxpool2d_i32(const int32_t *x, int32_t *out, int B, int C, int H, int W,
 int ds_avgpool_fix_i32(const int32_t *x, int32_t *out, int B, int C, int H, int W, int F, void *stream);
 
 /*
+ * Glue of the fp32 module path: y[i] = y[i] + r[i], then max(., 0) when relu != 0, in place and in
+ * one pass -- what a residual block's `out += identity; out = relu(out)` (two torch kernels, five
+ * passes over the tensor) computes, bit for bit (IEEE fp32 addition; a NaN stays a NaN).
+ * r may be NULL (ReLU only).  y and r must not overlap unless they are the same buffer.
+ */
+int ds_add_relu_f32(float *y, const float *r, long long n, int relu, void *stream);
+
+/*
  * Register-only issue-rate probe used for the roofline denominator.
  *   mode 0: shift + add (both on the integer ALU pipe)
  *   mode 1: shift + integer multiply-add (ALU pipe + FMA pipe)

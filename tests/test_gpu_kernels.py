@@ -955,3 +955,69 @@ def test_unoptimized_fp32_baseline_matches_torch(cuda_device):
         got = U.convert_to_unoptimized(model.float())(xin)
     assert isinstance(model[0], U.UnoptimizedConv2d) and isinstance(model[3], U.UnoptimizedLinear)
     assert float((got.double() - want).abs().max()) <= 1e-5 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("shape", [(3, 16, 12, 24, 3, 1, 1), (40, 64, 28, 128, 3, 1, 1), (9, 32, 14, 64, 1, 2, 0),
+                                   (2, 3, 32, 16, 7, 2, 3)], ids=["small", "ws3x3", "ws1x1s2", "stem7x7"])
+def test_module_fusion_hints_equal_the_unfused_ops(oracle, cuda_device, shape):
+    """`forward(x, residual=r, relu=True)` of the shift modules equals `F.relu(forward(x) + r)` bit for
+    bit: arbitrary fp32 residuals (not just fixed-point values), every kernel the convolution can
+    land on, and against the oracle's integer sums."""
+    from deepshift_b200 import modules
+    B, C, H, OC, k, s, p = shape
+    I, F = 4, 12
+    rng = np.random.default_rng(sum(shape))
+    conv = modules.Conv2dShift(C, OC, k, s, p, use_kernel=True, act_integer_bits=I, act_fraction_bits=F).to(cuda_device)
+    shift, sign = weights(rng, (OC, C, k, k), lo=-14)
+    with torch.no_grad():
+        conv.shift.copy_(_t(shift.astype(np.float32), cuda_device))
+        conv.sign.copy_(_t(sign.astype(np.float32), cuda_device))
+    x = _t(rng.normal(0, 2, (B, C, H, H)).astype(np.float32), cuda_device)
+    with torch.no_grad():
+        plain = conv(x)
+        r = _t(rng.normal(0, 3, tuple(plain.shape)).astype(np.float32), cuda_device)
+        assert torch.equal(conv(x, residual=r, relu=True), torch.relu(plain + r))
+        assert torch.equal(conv(x, residual=r), plain + r)
+        assert torch.equal(conv(x, relu=True), torch.relu(plain))
+    bias = oracle.to_fixed_conv(conv.bias.data.cpu().numpy(), I, F)
+    ref = oracle.conv2d(oracle.to_fixed_conv(x.cpu().numpy(), I, F), shift, sign, bias, (s, s), (p, p))
+    want = np.maximum(oracle.from_fixed(ref, F) + r.cpu().numpy(), np.float32(0))
+    assert np.array_equal(conv(x, residual=r, relu=True).cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 40, 300])
+def test_linear_module_fusion_hints(oracle, cuda_device, M):
+    """The same hints on LinearShift / LinearShiftQ, on every linear kernel (M <= 16, <= 64, larger)."""
+    from deepshift_b200 import modules, modules_q
+    rng = np.random.default_rng(M)
+    K, N = 256, 48
+    x = _t(rng.normal(0, 1, (M, K)).astype(np.float32), cuda_device)
+    r = _t(rng.normal(0, 2, (M, N)).astype(np.float32), cuda_device)
+    lin = modules.LinearShift(K, N, use_kernel=True, act_integer_bits=4, act_fraction_bits=12).to(cuda_device)
+    linq = modules_q.LinearShiftQ(K, N, use_kernel=True, act_integer_bits=4, act_fraction_bits=12).to(cuda_device)
+    with torch.no_grad():
+        for m in (lin, linq):
+            plain = m(x)
+            assert torch.equal(m(x, residual=r, relu=True), torch.relu(plain + r))
+            assert torch.equal(m(x, relu=True), torch.relu(plain))
+
+
+def test_add_relu_glue_kernel(cuda_device):
+    """ds_add_relu_f32: in place, equal to the torch ops bit for bit, ragged and unaligned lengths,
+    NaN kept, nothing written beyond n."""
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(5)
+    for n, off in [(1, 0), (7, 0), (4096, 0), (100003, 1), (64, 3)]:
+        base = _t(rng.normal(0, 1, n + off + 8).astype(np.float32), cuda_device)
+        r = _t(rng.normal(0, 1, n).astype(np.float32), cuda_device)
+        y = base[off:off + n]
+        want = torch.relu(y + r)
+        tail = base[off + n:].clone()
+        kernels.add_relu_f32_(y, r, relu=True)
+        assert torch.equal(y, want) and torch.equal(base[off + n:], tail)
+    y = _t(np.array([np.nan, -1.0, 2.0, -0.5], np.float32), cuda_device)
+    kernels.add_relu_f32_(y, None, relu=True)
+    out = y.cpu().numpy()
+    assert np.isnan(out[0]) and np.array_equal(out[1:], np.array([0, 2, 0], np.float32))
+    with pytest.raises(RuntimeError):
+        kernels.add_relu_f32_(y, torch.zeros(5, device=cuda_device), relu=True)

@@ -22,7 +22,9 @@ def test_networks_bit_exact_against_oracle(oracle, cuda_device, name, batch, kw)
     ref = R.forward(net, np_weights(ws), x.numpy())
     with torch.no_grad():
         y_mod = W.ModuleNet(net, ws, cuda_device).eval()(x.to(cuda_device)).cpu().numpy()
+        y_fused = W.ModuleNet(net, ws, cuda_device, fuse=True).eval()(x.to(cuda_device)).cpu().numpy()
     assert np.array_equal(y_mod, ref)
+    assert np.array_equal(y_fused, ref)
     for graph in (False, True):
         pipe = W.IntPipeline(net, ws, batch, cuda_device, use_graph=graph)
         assert np.array_equal(pipe.run(x.to(cuda_device)).cpu().numpy(), ref), graph
@@ -41,8 +43,10 @@ def test_resnet18_full_resolution_sample_against_oracle(oracle, cuda_device):
     y_pipe = pipe.run(x.to(cuda_device)).cpu().numpy()
     with torch.no_grad():
         y_mod = W.ModuleNet(net, ws, cuda_device).eval()(x.to(cuda_device)).cpu().numpy()
+        y_fused = W.ModuleNet(net, ws, cuda_device, fuse=True).eval()(x.to(cuda_device)).cpu().numpy()
     assert np.array_equal(y_pipe, ref)
     assert np.array_equal(y_mod, ref)
+    assert np.array_equal(y_fused, ref)
     assert np.array_equal(y_mod, y_pipe)
 
 
