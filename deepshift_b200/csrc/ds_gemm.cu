@@ -748,8 +748,11 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     // Small batches run on the integer pipe: up to 16 rows on the kernel that splits K across the
     // lanes of a warp, up to 64 rows on the block kernel with a 64-row tile (K split across CTAs
     // when nothing is fused into the epilogue).
+    // The 64-row tile also serves larger batches on the integer path while 128-row tiles would leave
+    // more than half of the SMs without one (a 256 x 512 -> 1000 classifier: 32 CTAs instead of 16).
+    const long long tiles128 = ((long long)(M + 127) / 128) * ((N + 127) / 128);
     if (M <= 16) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
-    if (M <= 64) {
+    if (M <= 64 || (!fp && tiles128 * 2 < 148)) {
         const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_INT, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
         if (rc != DS_ERR_UNSUPPORTED) return rc;
     }

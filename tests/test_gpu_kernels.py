@@ -52,6 +52,7 @@ def test_compress_api_matches_reference_signature(oracle, cuda_device):
 LINEAR_SHAPES = [(1, 1, 1), (3, 7, 5), (64, 784, 512), (130, 131, 129), (257, 500, 10), (64, 512, 10), (200, 96, 70),
                  (1000, 300, 40), (1, 4096, 33), (513, 29, 260),
                  (1, 4096, 4096), (64, 4096, 4096),     # the small-batch corner of the shift-GEMM sweep
+                 (256, 512, 1000),                      # a classifier head at the benchmark batch
                  (2, 640, 37), (5, 1031, 300), (8, 512, 1000), (13, 2048, 24), (16, 96, 4100), (17, 520, 130), (40, 3000, 70)]
 
 
