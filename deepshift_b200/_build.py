@@ -21,6 +21,11 @@ STAMP = os.path.join(LIB_DIR, "sources.sha256")
 CHECKED_LIB_PATH = os.path.join(LIB_DIR, "libdeepshift_b200_checked.so")
 CHECKED_STAMP = os.path.join(LIB_DIR, "sources_checked.sha256")
 CHECKED_FLAGS = ("-DDS_BOUNDS_CHECK",)
+# The timing flavour: the warp-specialised kernel counts, per warp of one CTA, the cycles spent
+# waiting at the hand-shake, staging and in the epilogue, and prints them (a diagnostic).
+TIMING_LIB_PATH = os.path.join(LIB_DIR, "libdeepshift_b200_timing.so")
+TIMING_STAMP = os.path.join(LIB_DIR, "sources_timing.sha256")
+TIMING_FLAGS = ("-DDS_WS_TIMING",)
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -44,8 +49,16 @@ def _digest():
     return h.hexdigest()
 
 
-def is_current(checked=False):
-    lib, stamp = (CHECKED_LIB_PATH, CHECKED_STAMP) if checked else (LIB_PATH, STAMP)
+def _flavour(checked, timing):
+    if checked:
+        return CHECKED_LIB_PATH, CHECKED_STAMP, CHECKED_FLAGS, "obj_checked"
+    if timing:
+        return TIMING_LIB_PATH, TIMING_STAMP, TIMING_FLAGS, "obj_timing"
+    return LIB_PATH, STAMP, (), "obj"
+
+
+def is_current(checked=False, timing=False):
+    lib, stamp = _flavour(checked, timing)[:2]
     try:
         with open(stamp) as fh:
             return os.path.exists(lib) and fh.read().strip() == _digest()
@@ -58,16 +71,15 @@ def nvcc_path():
     return cand if os.path.exists(cand) else None
 
 
-def build(force=False, verbose=False, extra_flags=(), checked=False):
+def build(force=False, verbose=False, extra_flags=(), checked=False, timing=False):
     """Compile the library if the sources changed.  Returns the library path.
 
     Every ``.cu`` file is compiled to an object file by its own nvcc process (they run side by
     side), then the objects are linked into the shared library.  ``checked=True`` builds the
-    bounds-checking flavour beside the normal one."""
-    lib_path, stamp = (CHECKED_LIB_PATH, CHECKED_STAMP) if checked else (LIB_PATH, STAMP)
-    if checked:
-        extra_flags = tuple(extra_flags) + CHECKED_FLAGS
-    if not force and is_current(checked):
+    bounds-checking flavour beside the normal one, ``timing=True`` the cycle-counting one."""
+    lib_path, stamp, flavour_flags, obj_name = _flavour(checked, timing)
+    extra_flags = tuple(extra_flags) + tuple(flavour_flags)
+    if not force and is_current(checked, timing):
         return lib_path
     # One builder at a time: the ranks of a multi-process job may all find the library stale at
     # once.  The others wait here and then find it current.
@@ -75,17 +87,17 @@ def build(force=False, verbose=False, extra_flags=(), checked=False):
     os.makedirs(LIB_DIR, exist_ok=True)
     with open(os.path.join(LIB_DIR, ".build.lock"), "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
-        if not force and is_current(checked):
+        if not force and is_current(checked, timing):
             return lib_path
-        return _build_locked(force, verbose, extra_flags, checked, lib_path, stamp)
+        return _build_locked(verbose, extra_flags, obj_name, lib_path, stamp)
 
 
-def _build_locked(force, verbose, extra_flags, checked, lib_path, stamp):
+def _build_locked(verbose, extra_flags, obj_name, lib_path, stamp):
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found and %s is missing or stale" % lib_path)
     os.makedirs(LIB_DIR, exist_ok=True)
-    obj_dir = os.path.join(LIB_DIR, "obj_checked" if checked else "obj")
+    obj_dir = os.path.join(LIB_DIR, obj_name)
     os.makedirs(obj_dir, exist_ok=True)
     env = dict(os.environ)
     env.pop("CC", None)
@@ -120,5 +132,6 @@ def _build_locked(force, verbose, extra_flags, checked, lib_path, stamp):
 
 if __name__ == "__main__":
     import sys
-    flags = [a for a in sys.argv[1:] if a != "--checked"]
-    print(build(force=True, verbose=True, extra_flags=flags, checked="--checked" in sys.argv))
+    flags = [a for a in sys.argv[1:] if a not in ("--checked", "--timing")]
+    print(build(force=True, verbose=True, extra_flags=flags, checked="--checked" in sys.argv,
+                timing="--timing" in sys.argv))

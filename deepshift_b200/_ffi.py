@@ -78,10 +78,12 @@ def lib():
     global _lib
     if _lib is None:
         # DEEPSHIFT_B200_CHECKED=1 selects the bounds-checking flavour of the library
+        # (DEEPSHIFT_B200_TIMING=1 the cycle-counting one, a diagnostic)
         checked = os.environ.get("DEEPSHIFT_B200_CHECKED", "") not in ("", "0")
-        path = _build.CHECKED_LIB_PATH if checked else _build.LIB_PATH
-        if not _build.is_current(checked) and _build.nvcc_path() is not None:
-            _build.build(checked=checked)
+        timing = not checked and os.environ.get("DEEPSHIFT_B200_TIMING", "") not in ("", "0")
+        path = _build.CHECKED_LIB_PATH if checked else (_build.TIMING_LIB_PATH if timing else _build.LIB_PATH)
+        if not _build.is_current(checked, timing) and _build.nvcc_path() is not None:
+            _build.build(checked=checked, timing=timing)
         if not os.path.exists(path):
             raise RuntimeError(
                 "deepshift_b200: CUDA library %s is missing and cannot be built (no nvcc); "

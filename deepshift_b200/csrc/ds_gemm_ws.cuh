@@ -22,6 +22,16 @@
 #pragma once
 #include "ds_gemm_common.cuh"
 
+// -DDS_WS_TIMING (the "timing" flavour of the library): every warp of CTA 1 counts the cycles it
+// spends waiting at the hand-shake, staging and in the epilogue, and prints them when the kernel
+// ends.  A diagnostic build; the normal build contains none of it.
+#ifdef DS_WS_TIMING
+#include <cstdio>
+#define WS_T(...) __VA_ARGS__
+#else
+#define WS_T(...)
+#endif
+
 namespace ds {
 namespace {
 
@@ -579,6 +589,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // stores -- also across item boundaries: while the consumers finish an output tile and run
         // its epilogue, the first k-tiles of the next item are already being staged.
         int item = blockIdx.x, seq = 0, git = 0;
+        WS_T(long long tw = 0, ts = 0, tt = 0, tl = 0, t0 = 0, t1 = 0; const long long tstart = clock64();)
         if (item < total_items) {
             WsItem cur = ws_item(p, item, BM, BN);
             int tile = cur.t_begin;
@@ -588,7 +599,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             issue_loads(tile, cur.m0);
             while (true) {
                 const int st = git % WS_STAGES;
+                WS_T(t0 = clock64();)
                 if (git >= WS_STAGES) mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u, &s.err);
+                WS_T(t1 = clock64(); tw += t1 - t0;)
                 const int k0 = tile * p.bk;
                 // Expanded weights are 0 beyond K, so the x values stored there need no care.
                 const bool last = !PRE && tile + 1 >= p.ntiles;
@@ -612,6 +625,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     }
                 }
                 warp_arrive(&s.full[st]);
+                WS_T(ts += clock64() - t1;)
                 ++git;
                 // next (item, k-tile)
                 if (++tile >= cur.t_end) {
@@ -622,11 +636,17 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     tile = cur.t_begin;
                     setup_item(cur);
                 }
+                WS_T(t0 = clock64();)
                 fill_table(tile);
                 if (CONV) producer_bar();
+                WS_T(t1 = clock64(); tt += t1 - t0;)
                 issue_loads(tile, cur.m0);
+                WS_T(tl += clock64() - t1;)
             }
         }
+        WS_T(if (blockIdx.x == 1 && (t & 31) == 0)
+                 printf("ws_timing producer warp %d: cycles %lld wait_empty %lld convert_store %lld table %lld issue_loads %lld k_tiles %d\n",
+                        t >> 5, clock64() - tstart, tw, ts, tt, tl, git);)
         if (s.err) *p.err_flag = 1;
         return;
     }
@@ -647,6 +667,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
     }
     float accf[kTM][TN];
     int git = 0, seq = 0;
+    WS_T(long long tw = 0, te = 0, t0 = 0; const long long tstart = clock64();)
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++seq) {
         const WsItem cur = ws_item(p, item, BM, BN);
         const int my_tiles = cur.t_end - cur.t_begin;
@@ -657,7 +678,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         int ndrains = 0, since = 0;
         for (int it = 0; it < my_tiles; ++it, ++git) {
             const int st = git % WS_STAGES;
+            WS_T(t0 = clock64();)
             mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u, &s.err);
+            WS_T(tw += clock64() - t0;)
             // The k-tile sizes of 3x3, 1x1 / 7x7 and 5x5 windows get fully unrolled loops.
             auto k_loop = [&](auto bk_tag) {
                 constexpr int CBK = decltype(bk_tag)::value;
@@ -714,6 +737,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // Negative weights of a column inside this unit's K range: counted by the producers while
         // they decode (tail_neg, the slots past K, belongs to the split that holds the last k-tile),
         // or read from the prefix counts that come with expanded weights.
+        WS_T(t0 = clock64();)
         const int* negc = s.negc[seq & 3];
         const int tailc = (cur.t_end == p.ntiles) ? p.tail_neg : 0;
         auto colcorr = [&](int col) -> int {
@@ -791,7 +815,11 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             consumer_bar();
             for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
         }
+        WS_T(te += clock64() - t0;)
     }
+    WS_T(if (blockIdx.x == 1 && lane == 0)
+             printf("ws_timing consumer warp %d: cycles %lld wait_full %lld epilogue %lld k_tiles %d\n", warp,
+                    clock64() - tstart, tw, te, git);)
     if (s.err) *p.err_flag = 1;
 }
 
