@@ -351,6 +351,14 @@ int ds_bounds_status(int *status, int *checked);
 int ds_bounds_debug_shrink_x(long long bytes);
 
 /*
+ * Timing build.  The library compiled with -DDS_WS_TIMING (flavour "timing":
+ * libdeepshift_b200_timing.so) has the warp-specialised convolution / linear kernel print, for every
+ * warp of its CTA 1, the cycles spent waiting at the producer / consumer hand-shake, staging and in
+ * the epilogue ("ws_timing ..." lines on stdout, one set per launch).  Same entry points, same results;
+ * a diagnostic, slower by the printing.
+ */
+
+/*
  * Number of kernels this library has launched in this process so far (a host-side counter;
  * diagnostics, no counterpart in the reference).  The difference across one forward pass is the
  * pass's kernel count, whatever path the launch heuristics took.
