@@ -13,7 +13,7 @@
 //     16-byte loads; its stores into the k-major stage are conflict-free.
 //   * The two groups meet only at mbarriers: full[s] (one arrival per producer warp, plus one per
 //     producer thread when its asynchronous weight copies land) and empty[s] (one per consumer
-//     warp) for each of the two stages.  Global-load latency, the decode chains
+//     warp) for each stage of the ring (two, or three on the 64-column tile).  Global-load latency, the decode chains
 //     and the stores of a stage all overlap the FFMA stream of the previous stage, so the
 //     FMA pipe no longer idles while "everybody stages".
 //
@@ -40,7 +40,13 @@ constexpr int WS_PROD = 256;   // producer threads
 constexpr int WS_NT = WS_CONS + WS_PROD;
 constexpr int WS_BM = 256;     // rows of x per CTA
 constexpr int WS_BKT = 28;     // largest k-tile
-constexpr int WS_STAGES = 2;
+// Stages of the ring: two on the 128-column tile (the accumulator slots take 128 KiB of shared
+// memory there), three on the 64-column tile, where the slots are half as large and the producers'
+// chain per k-tile is as long as the consumers' k-tile: with a third stage they never wait for `empty`.
+template <int TN>
+struct WsStages {
+    static constexpr int N = (TN == 4) ? 3 : 2;
+};
 // Register split after the roles part.  The CTA starts with 768 * 80 registers; what the
 // producers give back is all the consumers can take: a larger request would wait for registers
 // that never come.  Usual split 56 / 88 (256 * 24 >= 512 * 8).  The four-pixel staging mode and
@@ -62,16 +68,18 @@ template <int TN>
 struct WsSmem {
     static constexpr int BN = 16 * TN;
     static constexpr int AP = WS_BM + 4;
-    alignas(16) float a[WS_STAGES][WS_BKT][AP];  // x + 0.5
-    alignas(16) float b[WS_STAGES][WS_BKT][BN];  // +-2^-r
-    alignas(16) KEntry ktab[WS_STAGES][WS_BKT];
-    alignas(8) unsigned long long full[WS_STAGES];
-    alignas(8) unsigned long long empty[WS_STAGES];
+    static constexpr int STAGES = WsStages<TN>::N;
+    alignas(16) float a[STAGES][WS_BKT][AP];  // x + 0.5
+    alignas(16) float b[STAGES][WS_BKT][BN];  // +-2^-r
+    alignas(16) KEntry ktab[2][WS_BKT];       // by k-tile parity: written one k-tile ahead of its use
+    alignas(8) unsigned long long full[STAGES];
+    alignas(8) unsigned long long empty[STAGES];
     int lut0[256];  // float bits of the decoded weight per field value
-    // Negative weights per output column.  Four sets, used round-robin by item: the producers can
-    // be two items ahead of the consumers (items of a single k-tile), and a set is cleared by the
+    // Negative weights per output column.  NEGSETS sets, used round-robin by item: the producers can
+    // be STAGES items ahead of the consumers (items of a single k-tile), and a set is cleared by the
     // consumers only after their epilogue.
-    int negc[4][BN];
+    static constexpr int NEGSETS = (STAGES == 2) ? 4 : 8;
+    int negc[NEGSETS][BN];
     int err;
     int last_flag;  // split-K: this CTA arrived last at its tile's counter
     int accs[kTM * TN * WS_CONS];  // drained accumulators, [slot][consumer thread]
@@ -206,9 +214,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         int neg;
         s.lut0[f] = __float_as_int(decode_f32(uint32_t(f), p.dec, true, neg));
     }
-    for (int i = t; i < 4 * BN; i += WS_NT) (&s.negc[0][0])[i] = 0;
+    for (int i = t; i < S::NEGSETS * BN; i += WS_NT) (&s.negc[0][0])[i] = 0;
     if (t == 0) {
-        for (int i = 0; i < WS_STAGES; ++i) {
+        for (int i = 0; i < S::STAGES; ++i) {
             // one arrival per producer warp (x stored) and, with expanded weights, one per producer
             // thread when its asynchronous weight copies have landed
             mbar_init(&s.full[i], WS_PROD / 32 + (PRE ? WS_PROD : 0));
@@ -598,9 +606,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             if (CONV) producer_bar();
             issue_loads(tile, cur.m0);
             while (true) {
-                const int st = git % WS_STAGES;
+                const int st = git % S::STAGES;
                 WS_T(t0 = clock64();)
-                if (git >= WS_STAGES) mbar_wait(&s.empty[st], unsigned(git / WS_STAGES - 1) & 1u, &s.err);
+                if (git >= S::STAGES) mbar_wait(&s.empty[st], unsigned(git / S::STAGES - 1) & 1u, &s.err);
                 WS_T(t1 = clock64(); tw += t1 - t0;)
                 const int k0 = tile * p.bk;
                 // Expanded weights are 0 beyond K, so the x values stored there need no care.
@@ -614,7 +622,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
                     else store_x(ink_tag, std::false_type(), st, k0);
                 });
                 if (!PRE) {
-                    int* negc = s.negc[seq & 3];
+                    int* negc = s.negc[seq & (S::NEGSETS - 1)];
                     switch (p.dec.num) {
                         case 4: store_w(std::integral_constant<int, 4>(), st, negc); break;
                         case 5: store_w(std::integral_constant<int, 5>(), st, negc); break;
@@ -677,9 +685,9 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
             for (int j = 0; j < TN; ++j) accf[i][j] = kMagic;
         int ndrains = 0, since = 0;
         for (int it = 0; it < my_tiles; ++it, ++git) {
-            const int st = git % WS_STAGES;
+            const int st = git % S::STAGES;
             WS_T(t0 = clock64();)
-            mbar_wait(&s.full[st], unsigned(git / WS_STAGES) & 1u, &s.err);
+            mbar_wait(&s.full[st], unsigned(git / S::STAGES) & 1u, &s.err);
             WS_T(tw += clock64() - t0;)
             // The k-tile sizes of 3x3, 1x1 / 7x7 and 5x5 windows get fully unrolled loops.
             auto k_loop = [&](auto bk_tag) {
@@ -738,7 +746,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // they decode (tail_neg, the slots past K, belongs to the split that holds the last k-tile),
         // or read from the prefix counts that come with expanded weights.
         WS_T(t0 = clock64();)
-        const int* negc = s.negc[seq & 3];
+        const int* negc = s.negc[seq & (S::NEGSETS - 1)];
         const int tailc = (cur.t_end == p.ntiles) ? p.tail_neg : 0;
         auto colcorr = [&](int col) -> int {
             if (PRE) {
@@ -813,7 +821,7 @@ __global__ void __launch_bounds__(WS_NT, 1) ws_kernel(const GemmParams p)
         // a later item (the producers are filling other sets meanwhile).
         if (!PRE) {
             consumer_bar();
-            for (int i = t; i < BN; i += WS_CONS) s.negc[seq & 3][i] = 0;
+            for (int i = t; i < BN; i += WS_CONS) s.negc[seq & (S::NEGSETS - 1)][i] = 0;
         }
         WS_T(te += clock64() - t0;)
     }
