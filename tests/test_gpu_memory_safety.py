@@ -239,3 +239,38 @@ def test_bounds_checking_flavour_of_the_library(cuda_device):
     res = subprocess.run([sys.executable, script], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                          timeout=1200)
     assert res.returncode == 0 and "checked build: ok" in res.stdout, res.stdout[-3000:]
+
+
+def test_timing_flavour_prints_cycle_counters_and_computes_the_same(cuda_device):
+    """The library built with -DDS_WS_TIMING in a process of its own: one convolution on the
+    warp-specialised kernel gives the result of the normal flavour and leaves one "ws_timing" line per
+    warp of a CTA (16 consumer and 8 producer warps).  Skipped where that flavour was not built."""
+    import os
+    import subprocess
+    import sys
+    from deepshift_b200 import _build, _ffi, kernels
+    if not _build.is_current(timing=True):
+        pytest.skip("timing flavour not built")
+    code = (
+        "import numpy as np, torch\n"
+        "from deepshift_b200 import kernels, utils, _ffi\n"
+        "rng = np.random.default_rng(3)\n"
+        "x = torch.from_numpy(rng.integers(-30000, 30000, (40, 16, 28, 28)).astype(np.int32)).cuda()\n"
+        "shift = torch.from_numpy(rng.integers(-14, 1, (128, 16, 3, 3)).astype(np.float32))\n"
+        "sign = torch.from_numpy(rng.choice([-1., 0., 1.], (128, 16, 3, 3)).astype(np.float32))\n"
+        "cw = utils.compress_bits(shift, sign, device=x.device)\n"
+        "out = kernels.conv2d_fused(x, (128, 16, 3, 3), None, cw, 1, 1, act_bits=16)\n"
+        "torch.cuda.synchronize()\n"
+        "print('checksum', int(out.to(torch.int64).sum()), int((out.to(torch.int64) * 7 % 1000003).sum()))\n")
+    outs = {}
+    for flavour in ("", "1"):
+        env = dict(os.environ, DEEPSHIFT_B200_TIMING=flavour, PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        res = subprocess.run([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                             text=True, timeout=600)
+        assert res.returncode == 0, res.stdout[-3000:]
+        outs[flavour] = res.stdout
+    checks = {k: [l for l in v.splitlines() if l.startswith("checksum")] for k, v in outs.items()}
+    assert checks[""] and checks[""] == checks["1"]
+    assert "ws_timing" not in outs[""]
+    lines = [l for l in outs["1"].splitlines() if l.startswith("ws_timing")]
+    assert sum("consumer warp" in l for l in lines) == 16 and sum("producer warp" in l for l in lines) == 8, outs["1"][-2000:]

@@ -366,3 +366,13 @@ def test_reference_tree_calls_the_stub_with_the_right_arguments(monkeypatch):
     # B, C, H, W of the tensor kernels.py has already padded; OC; window; strides; no padding; bits, base, act_bits
     assert a[4:] == (2, 3, 10, 10, 5, 3, 3, 2, 2, 0, 0, 6, 0, 0, None)
     assert a[1:4] == (cw.data.data_ptr(), bias.data_ptr(), out.data_ptr())
+
+
+def test_library_flavours_have_their_own_files_and_flags():
+    """The normal, bounds-checking and timing flavours are three libraries with three stamps; only the
+    two diagnostic ones get an extra macro."""
+    from deepshift_b200 import _build
+    normal, checked, timing = _build._flavour(False, False), _build._flavour(True, False), _build._flavour(False, True)
+    assert len({normal[0], checked[0], timing[0]}) == 3 and len({normal[1], checked[1], timing[1]}) == 3
+    assert normal[2] == () and checked[2] == ("-DDS_BOUNDS_CHECK",) and timing[2] == ("-DDS_WS_TIMING",)
+    assert len({normal[3], checked[3], timing[3]}) == 3
