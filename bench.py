@@ -587,12 +587,24 @@ def run_case(args):
         raise SystemExit("bench.py needs a CUDA device: the shift kernels have no CPU fallback")
     kw = dict(bits=args.bits, dense=args.dense, act_bits=args.act_bits, iters=args.steps, warmup=args.warmup)
     kind, dims = args.case[0], [int(v) for v in args.case[1:]]
-    if kind == "gemm" and len(dims) == 3:
+    if kind == "all" and not dims:
+        # the whole grid of BASELINE configs[4] in one process, one JSON line per case
+        for dense in (False, True):
+            for bits in (2, 3, 4, 5):
+                for kn in (512, 1024, 2048, 4096):
+                    for M in (1, 64, 1024, 8192):
+                        print(json.dumps(run_gemm(M, kn, kn, bits=bits, dense=dense, act_bits=args.act_bits,
+                                                  iters=(20 if M <= 64 else 5), warmup=args.warmup)), flush=True)
+        for dense in (False, True):
+            for (C, H) in ((64, 56), (128, 28), (256, 14), (512, 7)):
+                print(json.dumps(run_conv(256, C, H, C, 3, 1, 1, bits=5, dense=dense, act_bits=args.act_bits, iters=5,
+                                          warmup=args.warmup)), flush=True)
+    elif kind == "gemm" and len(dims) == 3:
         print(json.dumps(run_gemm(*dims, **kw)))
     elif kind == "conv" and len(dims) == 7:
         print(json.dumps(run_conv(*dims, staged=args.staged, **kw)))
     else:
-        raise SystemExit("--case conv B C H OC K S P | --case gemm M K N")
+        raise SystemExit("--case conv B C H OC K S P | --case gemm M K N | --case all")
 
 
 def main():
@@ -605,7 +617,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--ref-seconds", type=float, default=150.0,
                     help="reference arm: stop starting new steps when the run would pass this many seconds")
-    ap.add_argument("--case", nargs="+", help="time one standalone layer: conv B C H OC K S P | gemm M K N")
+    ap.add_argument("--case", nargs="+",
+                    help="time one standalone layer: conv B C H OC K S P | gemm M K N; `all`: every case of configs[4]")
     ap.add_argument("--bits", type=int, default=5)
     ap.add_argument("--dense", action="store_true")
     ap.add_argument("--act-bits", type=int, default=16)

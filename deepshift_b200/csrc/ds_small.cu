@@ -6,7 +6,8 @@
 //
 //   * a warp owns CN neighbouring output columns and all M rows; its 32 lanes split K: lane l takes
 //     packed words l, l+32, ... of each of its rows (one coalesced 128-byte request per row and
-//     step; 16-byte requests per lane when rows are whole 16-byte groups), decodes each word's
+//     step; 16- or 8-byte requests per lane when rows are whole groups of four or two words, and
+//     16- or 8-byte requests on x when a word's weights are), decodes each word's
 //     fields once through a small lookup table in shared memory, and applies every weight to the M
 //     activations it meets (exact integer arithmetic: shift, then multiply by +-1 / +-2^k / 0);
 //   * when the columns alone do not fill the GPU, WPC warps of a CTA share a column group and split
@@ -23,7 +24,7 @@ constexpr int SM_WARPS = 8;
 constexpr int SM_THREADS = SM_WARPS * 32;
 
 template <int MR, int CN, int INK>
-__global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmParams p, int wpc, int vec4)
+__global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmParams p, int wpc, int vecw)
 {
     __shared__ int2 lut[256];                       // (right shift, multiplier) per field value
     __shared__ int part[SM_WARPS][MR * CN];         // partial sums of the warps that share a column group
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
     const int32_t* xi = static_cast<const int32_t*>(p.x);
     // one packed word of every column against the activations it meets
     const bool vecx = (num == 4) && (p.K % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 15u) == 0);
+    const bool pairx = !vecx && (num % 2 == 0) && (p.K % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.x) & 7u) == 0);
     auto word_step = [&](int w, const uint32_t (&word)[CN]) {
         const int k0 = w * num;
         if (vecx) {
@@ -78,6 +80,32 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
                 }
             return;
         }
+        if (pairx) {
+            // an even number of weights per word and rows of whole 8-byte groups: x in pairs
+            for (int j = 0; j < num; j += 2) {
+                const int k = k0 + j;
+                if (k >= p.K) break;  // K is even: k + 1 < K as well
+                int xv[MR][2];
+#pragma unroll
+                for (int m = 0; m < MR; ++m) {
+                    int2 r = make_int2(0, 0);
+                    if (m0 + m < p.M && DS_X_OK(p, xi + (size_t)(m0 + m) * p.K + k, 8))
+                        r = __ldg(reinterpret_cast<const int2*>(xi + (size_t)(m0 + m) * p.K + k));
+                    xv[m][0] = __float_as_int(operand_of<false, INK>(p, r.x));
+                    xv[m][1] = __float_as_int(operand_of<false, INK>(p, r.y));
+                    if (m0 + m >= p.M) xv[m][0] = xv[m][1] = 0;
+                }
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                    for (int c = 0; c < CN; ++c) {
+                        const int2 d = lut[(word[c] >> ((j + jj) * fw)) & fmask];
+#pragma unroll
+                        for (int m = 0; m < MR; ++m) acc[m][c] += (xv[m][jj] >> d.x) * d.y;
+                    }
+            }
+            return;
+        }
         for (int j = 0; j < num; ++j) {
             const int k = k0 + j;
             if (k >= p.K) break;
@@ -99,7 +127,26 @@ __global__ void __launch_bounds__(SM_THREADS) small_linear_kernel(const GemmPara
 
     if (n0 < p.N) {
         const int lanes = 32 * wpc, me = ksplit * 32 + lane;
-        if (vec4) {
+        if (vecw == 2) {
+            // rows are whole 8-byte groups: two words per lane and request
+            const int row2 = p.dec.row_len >> 1;
+            for (int q = me; q < row2; q += lanes) {
+                uint2 wq[CN];
+#pragma unroll
+                for (int c = 0; c < CN; ++c) {
+                    wq[c] = make_uint2(0, 0);
+                    if (n0 + c < p.N && DS_W_OK(p, reinterpret_cast<const uint2*>(p.packed + (size_t)(n0 + c) * p.dec.row_len) + q, 8))
+                        wq[c] = __ldg(reinterpret_cast<const uint2*>(p.packed + (size_t)(n0 + c) * p.dec.row_len) + q);
+                }
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    uint32_t word[CN];
+#pragma unroll
+                    for (int c = 0; c < CN; ++c) word[c] = e == 0 ? wq[c].x : wq[c].y;
+                    word_step(2 * q + e, word);
+                }
+            }
+        } else if (vecw == 4) {
             // rows are whole 16-byte groups: four words per lane and request
             const int row4 = p.dec.row_len >> 2;
             for (int q = me; q < row4; q += lanes) {
@@ -192,14 +239,16 @@ int launch_small(const GemmParams& p, cudaStream_t st)
     const int groups_per_cta = SM_WARPS / wpc;
     const long long gx = ((long long)groups + groups_per_cta - 1) / groups_per_cta;
     if (gx > 2147483647LL || row_blocks > 65535) return DS_ERR_RANGE;
-    const int vec4 = (p.dec.row_len % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.packed) & 15u) == 0);
+    // packed words per request: 4 or 2 where every row starts on such a boundary, else 1
+    const uintptr_t pw = reinterpret_cast<uintptr_t>(p.packed);
+    const int vecw = (p.dec.row_len % 4 == 0 && (pw & 15u) == 0) ? 4 : ((p.dec.row_len % 2 == 0 && (pw & 7u) == 0) ? 2 : 1);
     const dim3 grid((unsigned)gx, (unsigned)row_blocks);
     if (p.in_kind == DS_IN_I32)
-        small_linear_kernel<MR, CN, INK_I32><<<grid, SM_THREADS, 0, st>>>(p, wpc, vec4);
+        small_linear_kernel<MR, CN, INK_I32><<<grid, SM_THREADS, 0, st>>>(p, wpc, vecw);
     else if (p.in_kind == DS_IN_I32_CLAMP)
-        small_linear_kernel<MR, CN, INK_I32_CLAMP><<<grid, SM_THREADS, 0, st>>>(p, wpc, vec4);
+        small_linear_kernel<MR, CN, INK_I32_CLAMP><<<grid, SM_THREADS, 0, st>>>(p, wpc, vecw);
     else
-        small_linear_kernel<MR, CN, INK_F32><<<grid, SM_THREADS, 0, st>>>(p, wpc, vec4);
+        small_linear_kernel<MR, CN, INK_F32><<<grid, SM_THREADS, 0, st>>>(p, wpc, vecw);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
