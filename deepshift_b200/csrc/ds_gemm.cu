@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     };
 
     // ---- main loop: two shared buffers, register prefetch, one barrier per tile --------------
-    // gridDim.z > 1 (integer path, plain epilogue only): CTA z takes k-tiles [t_begin, t_end)
+    // gridDim.z > 1 (linear layers, plain epilogue only): CTA z takes k-tiles [t_begin, t_end)
     const int t_begin = blockIdx.z * p.tiles_per_split;
     const int t_end = min(p.ntiles, t_begin + p.tiles_per_split);
     fill_ktab(t_begin, 0);
@@ -402,11 +402,21 @@ __global__ void __launch_bounds__(NT, MODE == MODE_FP ? 1 : 2) gemm_kernel(const
     if (FP) drain();  // each thread reads back only its own slots below
 
     // ---- epilogue -----------------------------------------------------------------------------
-    if (!FP && gridDim.z > 1) {
-        // split along K: integer adds into the zeroed output commute, the bias goes in once
+    if (gridDim.z > 1) {
+        // split along K: integer adds into the zeroed output commute, the bias goes in once; on the
+        // FP32-pipe path every CTA adds the count of the negative weights it decoded (the slots
+        // past K belong to the range that holds the last k-tile)
         reduce_tile<TN, CONV>(
-            p, m0, n0, tm, tn, BM, BN, [&](int i, int j, long long) -> int { return acc[FP ? 0 : i][FP ? 0 : j]; },
-            [&](int col) -> int { return (blockIdx.z == 0 && p.bias && n0 + col < p.N) ? __ldg(p.bias + n0 + col) : 0; });
+            p, m0, n0, tm, tn, BM, BN,
+            [&](int i, int j, long long) -> int {
+                if (FP) return s.accs[(i * TN + j) * NT + t] - ndrains * kMagicBits;
+                return acc[FP ? 0 : i][FP ? 0 : j];
+            },
+            [&](int col) -> int {
+                int c = (blockIdx.z == 0 && p.bias && n0 + col < p.N) ? __ldg(p.bias + n0 + col) : 0;
+                if (FP) c += s.negc[col] - (t_end == p.ntiles ? p.tail_neg : 0);
+                return c;
+            });
         return;
     }
     store_tile<TN, CONV>(
@@ -471,7 +481,7 @@ int launch_cfg(GemmParams p, cudaStream_t st)
     p.splits = 1;
     p.tiles_per_split = p.ntiles;
     const bool plain = p.out_kind == DS_OUT_I32 && !p.relu && !p.requant && !p.round_f32 && !p.residual;
-    if (MODE == MODE_INT && AM == AM_LINEAR && plain && !p.gate && gx * gy < 148) {
+    if (AM == AM_LINEAR && plain && !p.gate && gx * gy < 148) {
         // Few output tiles (small batch): split K across gridDim.z until two CTAs per SM have work;
         // the partial sums meet through integer atomics in the zeroed output.
         int splits = 1;
@@ -752,6 +762,11 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     // more than half of the SMs without one (a 256 x 512 -> 1000 classifier: 32 CTAs instead of 16).
     const long long tiles128 = ((long long)(M + 127) / 128) * ((N + 127) / 128);
     if (M <= 16) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
+    if (fp && M <= 64) {
+        // a caller that bounds its activations gets the same tile on the FP32 pipe
+        const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_FP, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
+        if (rc != DS_ERR_UNSUPPORTED) return rc;
+    }
     if (M <= 64 || (!fp && tiles128 * 2 < 148)) {
         const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_INT, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
         if (rc != DS_ERR_UNSUPPORTED) return rc;
