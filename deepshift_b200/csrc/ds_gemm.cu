@@ -762,8 +762,10 @@ extern "C" int ds_linear_ex(const void* x, const int32_t* packed, const int32_t*
     // more than half of the SMs without one (a 256 x 512 -> 1000 classifier: 32 CTAs instead of 16).
     const long long tiles128 = ((long long)(M + 127) / 128) * ((N + 127) / 128);
     if (M <= 16) return launch_small_linear(p, static_cast<cudaStream_t>(stream));
-    if (fp && M <= 64) {
-        // a caller that bounds its activations gets the same tile on the FP32 pipe
+    const long long tiles256 = ((long long)(M + 255) / 256) * ((N + 127) / 128);
+    if (fp && (M <= 64 || tiles256 * 4 < 148)) {
+        // a caller that bounds its activations gets the same tile on the FP32 pipe (also larger
+        // batches whose 256-row tiles would cover less than a quarter of the SMs)
         const int rc = launch_cfg<256, 8, 32, 4, 16, MODE_FP, AM_LINEAR>(p, static_cast<cudaStream_t>(stream));
         if (rc != DS_ERR_UNSUPPORTED) return rc;
     }
