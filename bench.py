@@ -269,7 +269,8 @@ def run_ours(args, rank, world, local):
     value = world * B * args.steps / (ms_total * 1e-3)
 
     # ---- end to end through the drop-in modules, host buffers, copies inside the timed region
-    # (the ReLUs and residual additions that follow a shift layer go to its forward as fusion hints)
+    # (the ReLUs and residual additions that follow a shift layer go to its forward as fusion hints,
+    # the max pool runs on the library's fp32 pooling kernel)
     model = W.ModuleNet(net, ws, dev, fuse=True).eval()
     model_plain = W.ModuleNet(net, ws, dev, fuse=False).eval()
     y_host = torch.empty((B, net.layers[-1].cout), dtype=torch.float32).pin_memory()
@@ -425,7 +426,8 @@ def run_ours(args, rank, world, local):
         "cpu_baseline": ({"value": cpu_val, "unit": UNIT, **cpu_info} if cpu_info else None),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": y_host.numel() * 4,
                 "api": "ModuleNet of LinearShift/Conv2dShift(use_kernel=True), pinned host input -> host logits; "
-                       "ReLU / residual add after a shift layer passed to its forward as fusion hints",
+                       "ReLU / residual add after a shift layer passed to its forward as fusion hints, "
+                       "max pool on the library's fp32 pooling kernel",
                 "without_fusion_hints": e2e_plain, "steps": e2e_steps},
         "parity": parity,
         "sweep": sweep,

@@ -57,6 +57,7 @@ _SIGNATURES = {
     "ds_quantize_f32": [_VP, _VP, _LL, _I, _I, _I, _VP],
     "ds_maxpool2d_i32": [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ds_add_relu_f32": [_VP, _VP, _LL, _I, _VP],
+    "ds_maxpool2d_f32": [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ds_avgpool_fix_i32": [_VP, _VP, _I, _I, _I, _I, _I, _VP],
     "ds_pipe_peak": [_I, _I, ctypes.POINTER(ctypes.c_double), _VP],
     "ds_last_kernel_error": [ctypes.POINTER(ctypes.c_int)],

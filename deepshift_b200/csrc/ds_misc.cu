@@ -45,10 +45,28 @@ __global__ void quantize_kernel(const float* __restrict__ x, int32_t* __restrict
     }
 }
 
-// Max pooling on int32 NCHW; positions outside the image do not take part (as with
-// torch.nn.functional.max_pool2d's implicit -inf padding).  Monotone, hence identical to pooling
-// the fp32 values int / 2^F and converting back.
-__global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out, long long total, int H,
+// Element types of the max pools: int32 codes, or fp32 values with torch's rule that a NaN in the
+// window is the result.
+template <typename T>
+struct Pool;
+template <>
+struct Pool<int32_t> {
+    using V4 = int4;
+    static __device__ __forceinline__ int32_t lowest() { return INT_MIN; }
+    static __device__ __forceinline__ int32_t mx(int32_t a, int32_t b) { return max(a, b); }
+};
+template <>
+struct Pool<float> {
+    using V4 = float4;
+    static __device__ __forceinline__ float lowest() { return __int_as_float(0xff800000); }  // -inf
+    static __device__ __forceinline__ float mx(float a, float b) { return (b > a || b != b) ? b : a; }
+};
+
+// Max pooling on NCHW; positions outside the image do not take part (as with
+// torch.nn.functional.max_pool2d's implicit -inf padding).  On int32 codes: monotone, hence identical
+// to pooling the fp32 values int / 2^F and converting back.
+template <typename T>
+__global__ void maxpool_kernel(const T* __restrict__ x, T* __restrict__ out, long long total, int H,
                                int W, int OH, int OW, int k, int st, int pad)
 {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -57,14 +75,14 @@ __global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restric
         const long long r = i / OW;
         const int oh = int(r % OH);
         const long long bc = r / OH;
-        const int32_t* src = x + bc * H * W;
-        int best = INT_MIN;
+        const T* src = x + bc * H * W;
+        T best = Pool<T>::lowest();
         for (int kh = 0; kh < k; ++kh) {
             const int ih = oh * st - pad + kh;
             if (unsigned(ih) >= unsigned(H)) continue;
             for (int kw = 0; kw < k; ++kw) {
                 const int iw = ow * st - pad + kw;
-                if (unsigned(iw) < unsigned(W)) best = max(best, __ldg(src + ih * W + iw));
+                if (unsigned(iw) < unsigned(W)) best = Pool<T>::mx(best, __ldg(src + ih * W + iw));
             }
         }
         out[i] = best;
@@ -74,9 +92,12 @@ __global__ void maxpool_kernel(const int32_t* __restrict__ x, int32_t* __restric
 // The 3x3 / stride 2 / padding 1 pool of the ResNet stem when W is a multiple of 8 and both
 // tensors are 16-byte aligned: a thread produces four neighbouring outputs from, per input row,
 // two 16-byte loads and the one value to their left (9 loads instead of 36), one 16-byte store.
-__global__ void __launch_bounds__(256) maxpool3s2_quad_kernel(const int32_t* __restrict__ x, int32_t* __restrict__ out,
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool3s2_quad_kernel(const T* __restrict__ x, T* __restrict__ out,
                                                               long long quads, int H, int W, int OH, int OW)
 {
+    using V4 = typename Pool<T>::V4;
+    auto mx = [](T a, T b) { return Pool<T>::mx(a, b); };
     const int qw = OW / 4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < quads;
          i += (long long)gridDim.x * blockDim.x) {
@@ -84,22 +105,24 @@ __global__ void __launch_bounds__(256) maxpool3s2_quad_kernel(const int32_t* __r
         const long long r = i / qw;
         const int oh = int(r % OH);
         const long long bc = r / OH;
-        const int32_t* src = x + bc * H * W + 8 * q;
-        int4 best = make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
+        const T* src = x + bc * H * W + 8 * q;
+        const T lo = Pool<T>::lowest();
+        V4 best;
+        best.x = best.y = best.z = best.w = lo;
 #pragma unroll
         for (int kh = 0; kh < 3; ++kh) {
             const int ih = 2 * oh - 1 + kh;
             if (unsigned(ih) >= unsigned(H)) continue;
-            const int32_t* row = src + (long long)ih * W;
-            const int4 a = __ldg(reinterpret_cast<const int4*>(row));
-            const int4 b = __ldg(reinterpret_cast<const int4*>(row) + 1);
-            const int left = q > 0 ? __ldg(row - 1) : INT_MIN;
-            best.x = max(best.x, max(left, max(a.x, a.y)));
-            best.y = max(best.y, max(a.y, max(a.z, a.w)));
-            best.z = max(best.z, max(a.w, max(b.x, b.y)));
-            best.w = max(best.w, max(b.y, max(b.z, b.w)));
+            const T* row = src + (long long)ih * W;
+            const V4 a = __ldg(reinterpret_cast<const V4*>(row));
+            const V4 b = __ldg(reinterpret_cast<const V4*>(row) + 1);
+            const T left = q > 0 ? __ldg(row - 1) : lo;
+            best.x = mx(best.x, mx(left, mx(a.x, a.y)));
+            best.y = mx(best.y, mx(a.y, mx(a.z, a.w)));
+            best.z = mx(best.z, mx(a.w, mx(b.x, b.y)));
+            best.w = mx(best.w, mx(b.y, mx(b.z, b.w)));
         }
-        *reinterpret_cast<int4*>(out + (bc * OH + oh) * OW + 4 * q) = best;
+        *reinterpret_cast<V4*>(out + (bc * OH + oh) * OW + 4 * q) = best;
     }
 }
 
@@ -227,8 +250,8 @@ extern "C" int ds_quantize_f32(const float* x, int32_t* out, long long n, int ki
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
 }
 
-extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, int H, int W, int k, int stride,
-                                int pad, void* stream)
+template <typename T>
+static int maxpool2d_run(const T* x, T* out, int B, int C, int H, int W, int k, int stride, int pad, void* stream)
 {
     if (!x || !out || B < 0 || C <= 0 || H <= 0 || W <= 0 || k <= 0 || stride <= 0 || pad < 0 || 2 * pad > k)
         return DS_ERR_BAD_ARG;
@@ -242,17 +265,29 @@ extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, in
         const long long quads = total / 4;  // OW = W / 2 is a multiple of 4
         const long long wantq = (quads + threads - 1) / threads;
         const int blocksq = int(wantq > 148 * 64 ? 148 * 64 : wantq);
-        maxpool3s2_quad_kernel<<<blocksq, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, quads, H, W, OH,
-                                                                                          OW);
+        maxpool3s2_quad_kernel<T><<<blocksq, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, quads, H, W,
+                                                                                             OH, OW);
         note_launch();
         return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
     }
     const long long want = (total + threads - 1) / threads;
     const int blocks = int(want > 148 * 32 ? 148 * 32 : want);
-    maxpool_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, total, H, W, OH, OW, k,
-                                                                            stride, pad);
+    maxpool_kernel<T><<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(x, out, total, H, W, OH, OW, k,
+                                                                               stride, pad);
     note_launch();
     return cudaGetLastError() == cudaSuccess ? DS_OK : DS_ERR_CUDA;
+}
+
+extern "C" int ds_maxpool2d_i32(const int32_t* x, int32_t* out, int B, int C, int H, int W, int k, int stride,
+                                int pad, void* stream)
+{
+    return maxpool2d_run<int32_t>(x, out, B, C, H, W, k, stride, pad, stream);
+}
+
+extern "C" int ds_maxpool2d_f32(const float* x, float* out, int B, int C, int H, int W, int k, int stride, int pad,
+                                void* stream)
+{
+    return maxpool2d_run<float>(x, out, B, C, H, W, k, stride, pad, stream);
 }
 
 // y = relu?(y + r) in place, four elements per thread where the pointers allow.

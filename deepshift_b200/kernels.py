@@ -293,6 +293,21 @@ def maxpool2d_i32(input, kernel_size, stride, padding=0, out=None):
     return out
 
 
+def maxpool2d_f32(input, kernel_size, stride, padding=0):
+    """``F.max_pool2d(input, kernel_size, stride, padding)`` on fp32 NCHW, bit for bit (square window, no
+    dilation, floor mode), on this library's pooling kernels."""
+    _check_tensor(input, "input", torch.float32)
+    B, C, H, W = input.shape
+    OH = (H + 2 * padding - kernel_size) // stride + 1
+    OW = (W + 2 * padding - kernel_size) // stride + 1
+    out = torch.empty([B, C, OH, OW], dtype=torch.float32, device=input.device)
+    with torch.cuda.device(input.device):
+        rc = _ffi.lib().ds_maxpool2d_f32(input.data_ptr(), out.data_ptr(), B, C, H, W, kernel_size, stride,
+                                         padding, _stream_ptr(input.device))
+    _ffi.check(rc, "maxpool2d_f32")
+    return out
+
+
 def add_relu_f32_(y, residual=None, relu=False):
     """In place, one pass: ``y += residual`` (when given), then ``y = relu(y)`` (when asked) -- the
     fp32 glue after a shift layer in a residual block, bit-identical to the two torch ops."""

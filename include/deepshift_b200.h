@@ -217,6 +217,15 @@ int ds_avgpool_fix_i32(const int32_t *x, int32_t *out, int B, int C, int H, int 
 int ds_add_relu_f32(float *y, const float *r, long long n, int relu, void *stream);
 
 /*
+ * Glue of the fp32 module path: F.max_pool2d on fp32 NCHW (square window, symmetric padding, no
+ * dilation, floor mode; a NaN in the window is the result, as in torch).  Same kernels as
+ * ds_maxpool2d_i32; the 3x3 / stride 2 / padding 1 pool of a ResNet stem takes a quarter of the time of
+ * torch's kernel.
+ */
+int ds_maxpool2d_f32(const float *x, float *out, int B, int C, int H, int W, int k, int stride, int pad,
+                     void *stream);
+
+/*
  * Register-only issue-rate probe used for the roofline denominator.
  *   mode 0: shift + add (both on the integer ALU pipe)
  *   mode 1: shift + integer multiply-add (ALU pipe + FMA pipe)

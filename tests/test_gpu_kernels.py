@@ -1022,3 +1022,18 @@ def test_add_relu_glue_kernel(cuda_device):
     assert np.isnan(out[0]) and np.array_equal(out[1:], np.array([0, 2, 0], np.float32))
     with pytest.raises(RuntimeError):
         kernels.add_relu_f32_(y, torch.zeros(5, device=cuda_device), relu=True)
+
+
+@pytest.mark.parametrize("shape,k,s,p", [((3, 5, 32, 32), 3, 2, 1), ((2, 4, 112, 112), 3, 2, 1), ((2, 3, 28, 28), 2, 2, 0),
+                                         ((2, 3, 15, 13), 3, 1, 1), ((1, 2, 9, 9), 3, 2, 1), ((2, 2, 24, 24), 5, 3, 2)])
+def test_fp32_max_pool_glue_equals_torch(cuda_device, shape, k, s, p):
+    """ds_maxpool2d_f32 against F.max_pool2d, bit for bit: the four-outputs-per-thread kernel of the stem's
+    pool (W a multiple of 8) and the general one, negative values at the padded border, a NaN."""
+    import torch.nn.functional as F
+    from deepshift_b200 import kernels
+    rng = np.random.default_rng(sum(shape) + k)
+    x = _t(rng.normal(-3, 2, shape).astype(np.float32), cuda_device)   # mostly negative: padding must not win
+    assert torch.equal(kernels.maxpool2d_f32(x, k, s, p), F.max_pool2d(x, k, s, p))
+    x[0, 0, 1, 2] = float('nan')
+    got, want = kernels.maxpool2d_f32(x, k, s, p), F.max_pool2d(x, k, s, p)
+    assert torch.equal(torch.isnan(got), torch.isnan(want)) and torch.equal(torch.nan_to_num(got), torch.nan_to_num(want))
