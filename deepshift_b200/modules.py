@@ -235,10 +235,11 @@ class Conv2dShift(_ConvNdShift):
                 raise RuntimeError("the shift convolution kernel supports neither dilation nor groups")
             x = input.float().contiguous()
             in_kind, act_bits = _ffi.IN_F32_CONV, 0
-            if self.kernel_size[0] * self.kernel_size[1] >= 25:
-                # a large window reads every input value many times: quantise once, in its own pass;
-                # the codes are final (round_to_fixed is not idempotent for one integer bit), so the
-                # kernel gets them as plain int32 with their bound
+            if utils.quantise_in_own_pass(self.kernel_size, self.out_channels):
+                # the kernel stages every input value once per filter tap and per tile of 128 output
+                # channels: from 9 such uses on, quantising once in a pass of its own is cheaper than
+                # quantising at every use; the codes are final (round_to_fixed is not idempotent for
+                # one integer bit), so the kernel gets them as plain int32 with their bound
                 x = kernels.quantize(x, self.act_integer_bits, self.act_fraction_bits, like_conv=True)
                 in_kind, act_bits = _ffi.IN_I32, utils.code_bits(self.act_integer_bits, self.act_fraction_bits)
             out = kernels.conv2d_fused(x, tuple(self.shift.shape), self._bias_fixed(like_conv=True),

@@ -223,8 +223,9 @@ class Conv2dShiftQ(_ConvNdShiftQ):
                 raise RuntimeError("the shift convolution kernel supports neither dilation nor groups")
             x = input.float().contiguous()
             in_kind, act_bits = _ffi.IN_F32_CONV, 0
-            if self.kernel_size[0] * self.kernel_size[1] >= 25:
-                # a large window reads every input value many times: quantise once, in its own pass
+            if utils.quantise_in_own_pass(self.kernel_size, self.out_channels):
+                # every input value is staged once per filter tap and tile of 128 output channels:
+                # from 9 uses on, quantise once, in a pass of its own
                 x = self._input_codes(x)
                 in_kind, act_bits = _ffi.IN_I32, self._act_bits()
             out = kernels.conv2d_fused(x, tuple(self.weight.shape), self._bias_fixed(), self._packed(x.device),

@@ -18,6 +18,14 @@ def round_to_fixed(input, integer_bits=16, fraction_bits=16):
     return torch.clamp(rounded, -bound, bound - 1)
 
 
+def quantise_in_own_pass(kernel_size, out_channels):
+    """Whether a shift convolution with fp32 input should quantise it in a separate pass: the
+    convolution kernel converts a value every time it stages it, once per filter tap and per tile
+    of 128 output channels; a pass of its own costs one read and one write of the tensor."""
+    uses = kernel_size[0] * kernel_size[1] * ((out_channels + 127) // 128)
+    return uses >= 9
+
+
 def code_bits(integer_bits, fraction_bits):
     """Bits b such that every int32 code of round_to_fixed(., I, F) * 2^F lies in
     [-2^(b-1), 2^(b-1)]: I + F, or F + 2 for one integer bit (codes -2^(F+1), -2^F, 0)."""
