@@ -357,8 +357,8 @@ class IntPipeline(_Pipeline):
                 xin = t[src]
                 in_fp32 = fp32[src]
                 if op == 'conv':
-                    if in_fp32 and L.k * L.k >= 25:
-                        # a large window reads every input value many times: quantise it once in a
+                    if in_fp32 and utils.quantise_in_own_pass((L.k, L.k), L.cout):
+                        # every input value would be converted many times: quantise it once in a
                         # pass of its own instead of inside the convolution's staging code
                         xq = torch.empty(xin.shape, dtype=torch.int32, device=dev)
                         self.calls.append(('quant', xin, xq))
